@@ -91,7 +91,7 @@ def plan_cache(needs: Sequence[Union[Need, Sequence[Need]]], cache_of: Sequence[
 class KVView:
     """What an attention-like mixer gets: its layer's pool, and the page table
     of the step's sequences (device int32 [B, P])."""
-    pool: torch.Tensor                 # [pages, 2, kv heads, page_size, head_dim]
+    pool: torch.Tensor                 # [pages, 2, kv heads, page_size, head_dim]; [pages, page elements] if need.uneven
     page_table: torch.Tensor
     page_size: int
     writable: bool
@@ -140,7 +140,10 @@ class SequenceCache:
         self.storage: Dict[int, torch.Tensor] = {}
         for gi, g in enumerate(plan.groups):
             if isinstance(g.need, KVNeed):
-                shape = (g.n_layers, max(n_pages, 1), 2, g.need.n_kv_heads, page_size, g.need.head_dim)
+                if g.need.uneven:
+                    shape = (g.n_layers, max(n_pages, 1), g.need.n_kv_heads * page_size * (g.need.head_dim + g.need.value_dim))
+                else:
+                    shape = (g.n_layers, max(n_pages, 1), 2, g.need.n_kv_heads, page_size, g.need.head_dim)
                 self.storage[gi] = torch.zeros(shape, dtype=dtype, device=self.device)
             else:
                 shape = (g.n_layers, max(n_slots, 1)) + tuple(g.need.shape)
@@ -253,9 +256,10 @@ class SequenceCache:
     def _give_back(self, slot: int, seq: _Slot) -> None:
         length = int(self._len[slot])
         for gi in self.windowed:
-            window = self.plan.groups[gi].need.window
-            first_needed = max(0, length - window + 1)     # the next token reads keys from here on
-            for blk in range(min(first_needed // self.page_size, len(seq.pages[gi]))):
+            need = self.plan.groups[gi].need
+            first_needed = max(0, length - need.window + 1)     # the next token reads keys from here on
+            kept = -(-need.keep_first // self.page_size)        # blocks that hold one of the kept first tokens
+            for blk in range(kept, min(first_needed // self.page_size, len(seq.pages[gi]))):
                 if seq.pages[gi][blk] is not None:
                     self.pages[gi].give(seq.pages[gi][blk])
                     seq.pages[gi][blk] = None
@@ -315,12 +319,25 @@ class SequenceCache:
     # ---- inspection ---------------------------------------------------------------
     def dump_slot(self, slot: int) -> Dict[int, torch.Tensor]:
         """Contents of a sequence for tests: per KV group [layers, 2, length, kv heads, head_dim]
-        (rows of pages that were given back are zero), per state group [layers, ...]."""
+        (rows of pages that were given back are zero; a group whose values differ in size from its keys
+        gives a pair (keys [layers, length, kv heads, head_dim], values [layers, length, kv heads, v_dim])),
+        per state group [layers, ...]."""
         seq = self._get(slot)
         out: Dict[int, torch.Tensor] = {}
         for gi, g in enumerate(self.plan.groups):
             st = self.storage[gi]
-            if isinstance(g.need, KVNeed):
+            if isinstance(g.need, KVNeed) and g.need.uneven:
+                L, nkv, dk, dv, ps = int(self._len[slot]), g.need.n_kv_heads, g.need.head_dim, g.need.value_dim, self.page_size
+                ks = torch.zeros((g.n_layers, L, nkv, dk), dtype=st.dtype, device=st.device)
+                vs = torch.zeros((g.n_layers, L, nkv, dv), dtype=st.dtype, device=st.device)
+                for blk, page in enumerate(seq.pages[gi]):
+                    lo, hi = blk * ps, min(L, (blk + 1) * ps)
+                    if page is None or lo >= hi:
+                        continue
+                    ks[:, lo:hi] = st[:, page, :nkv * ps * dk].view(-1, nkv, ps, dk)[:, :, :hi - lo].permute(0, 2, 1, 3)
+                    vs[:, lo:hi] = st[:, page, nkv * ps * dk:].view(-1, nkv, ps, dv)[:, :, :hi - lo].permute(0, 2, 1, 3)
+                out[gi] = (ks, vs)
+            elif isinstance(g.need, KVNeed):
                 L = int(self._len[slot])
                 rows = torch.zeros((g.n_layers, 2, L, g.need.n_kv_heads, g.need.head_dim), dtype=st.dtype,
                                    device=st.device)

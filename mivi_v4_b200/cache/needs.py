@@ -13,10 +13,23 @@ import torch
 class KVNeed:
     """Keys and values that grow by one row per token.  ``window`` > 0: only the
     last ``window`` tokens are ever read, so pages that lie wholly before them
-    are given back while the sequence is still running."""
+    are given back while the sequence is still running; ``keep_first`` tokens at the start of the sequence
+    stay readable for good, so the pages that hold any of them are never given back.  ``v_dim`` > 0: values
+    of another size than the keys' ``head_dim``; a page is then one flat row, the keys [kv head][row][head_dim]
+    followed by the values [kv head][row][v_dim]."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    v_dim: int = 0
+    keep_first: int = 0
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_dim or self.head_dim
+
+    @property
+    def uneven(self) -> bool:
+        return self.value_dim != self.head_dim
 
 
 @dataclass(frozen=True)

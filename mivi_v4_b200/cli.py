@@ -128,7 +128,7 @@ def cmd_info(a) -> int:
     from .weights import read_model_headers
     cfg = read_config_json(a.model)
     config, spec = describe_config(cfg)
-    print(f"architecture: {cfg['architectures'][0]}")
+    print(f"architecture: {(cfg.get('architectures') or [cfg.get('architecture')])[0]}")
     for k, v in config.to_dict().items():
         print(f"  {k}: {v}")
     for k in ("head_dim", "kv_dim", "ff_dim", "attn_layer_ids", "conv_layer_ids"):

@@ -1,6 +1,7 @@
 from .errors import ConfigError
 from .lfm2 import Lfm2Config, read_config_json
+from .votavik import VotavikConfig
 from .registry import Architecture, architecture_for, known_architectures, register_architecture
 
-__all__ = ["ConfigError", "Lfm2Config", "read_config_json", "Architecture", "architecture_for",
+__all__ = ["ConfigError", "Lfm2Config", "VotavikConfig", "read_config_json", "Architecture", "architecture_for",
            "known_architectures", "register_architecture"]

@@ -36,11 +36,14 @@ def known_architectures() -> list:
 
 
 def architecture_for(config_dict: dict) -> Architecture:
-    """The entry for config.json's ``architectures[0]``."""
+    """The entry for config.json's ``architectures[0]``, or for its ``architecture`` (one name) where a
+    configuration says it that way."""
     archs = config_dict.get("architectures")
+    if archs is None and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise ConfigError(
-            "config.json has no 'architectures' list; known architectures: "
+            "config.json has no 'architectures' list and no 'architecture' name; known architectures: "
             + ", ".join(known_architectures()))
     name = archs[0]
     if name not in _ARCHITECTURES:

@@ -1,0 +1,222 @@
+// Softmax attention over the paged cache with the variations that a grouped-query layer may carry:
+//   * keys and values of different sizes (dk, dv);
+//   * a root-mean-square norm over the WHOLE q projection and the whole k projection (all heads
+//     at once), before the rotation;
+//   * a rotation of the first rot_dims elements of every head only, element i paired with
+//     i + rot_dims/2;
+//   * capped scores: s <- cap * tanh(s / cap);
+//   * a sliding window that keeps the first tokens: query i reads key j <= i if i - j < window or
+//     j < keep_first;
+//   * a sink: a learned number per head whose exponential joins the softmax's denominator, with no
+//     value of its own;
+//   * a gate per token and head, sigmoid of a logit, on the head's output.
+// Each is a parameter (0 or null turns it off).
+//
+// Cache layout of one layer's page: [kv head][row][dk] keys, then [kv head][row][dv] values; with
+// dk == dv this is the layout [2][kv head][row][hd] of the library's other attention kernels.
+#include "common.cuh"
+
+#define AS_MAX_DIM 256
+
+// ------------------------------------------------ prepare q, k, v of a step's tokens
+// One block per token.  proj: 32-bit rows [q (nh*dk) | k (nkv*dk) | v (nkv*dv) | ...] with row
+// stride ld.  q goes to q_out in the model's dtype, k and v into the token's row of its page.
+template <typename T>
+__global__ void __launch_bounds__(128)
+qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ wq,
+                        const float* __restrict__ wk, float eps, int rot_dims, const float* __restrict__ inv_freq,
+                        const int* __restrict__ positions, const int* __restrict__ seq_of,
+                        const int* __restrict__ page_table, int table_stride, int page_shift, T* __restrict__ pool,
+                        long long page_stride, T* __restrict__ q_out, int nh, int nkv, int dk, int dv) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const int n = blockIdx.x;
+    const float* row = proj + (size_t)n * ld;
+    const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv;
+    const float* qr = row;
+    const float* kr = row + nq;
+    const float* vr = kr + nk;
+    float sq = 0.f, sk = 0.f;
+    for (int e = threadIdx.x; e < nq; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
+    const float q_scale = wq ? 1.0f / sqrtf(mv_block_sum(sq, scratch) / (float)nq + eps) : 1.f;
+    const float k_scale = wk ? 1.0f / sqrtf(mv_block_sum(sk, scratch) / (float)nk + eps) : 1.f;
+    const int pos = positions[n];
+    const int page_size = 1 << page_shift;
+    const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
+    const int prow = pos & (page_size - 1);
+    T* kpage = pool + (size_t)page * page_stride;
+    T* vpage = kpage + (size_t)nkv * page_size * dk;
+    const bool page_ok = mv_page_ok(page);
+    const int half = rot_dims >> 1;
+    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+        const bool is_q = e < nq;
+        const int f = is_q ? e : e - nq;
+        const float* src = is_q ? qr : kr;
+        const float* w = is_q ? wq : wk;
+        const float sc = is_q ? q_scale : k_scale;
+        const int head = f / dk, d = f - head * dk;
+        float a = src[f] * sc * (w ? w[f] : 1.f);
+        if (d < rot_dims) {
+            // element d < half pairs with d + half: (u, v) -> (u cos - v sin, v cos + u sin)
+            const int i = d < half ? d : d - half;
+            const int fp = d < half ? f + half : f - half;
+            const float b = src[fp] * sc * (w ? w[fp] : 1.f);
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            a = d < half ? a * cs - b * sn : a * cs + b * sn;
+        }
+        if (is_q)
+            q_out[(size_t)n * nq + f] = mv_from_f32<T>(a);
+        else if (page_ok)
+            kpage[((size_t)head * page_size + prow) * dk + d] = mv_from_f32<T>(a);
+    }
+    if (page_ok)
+        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+            const int head = e / dv, d = e - head * dv;
+            vpage[((size_t)head * page_size + prow) * dv + d] = mv_from_f32<T>(vr[e]);
+        }
+}
+
+MV_GUARD_SETTER(attention_sink)
+
+MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const float* wk, float eps, int rot_dims,
+                               const float* inv_freq, const int* positions, const int* seq_of, const int* page_table,
+                               int table_stride, int page_size, void* pool, long long page_stride, void* q_out,
+                               int dtype, int N, int nh, int nkv, int dk, int dv, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if ((page_size & (page_size - 1)) || rot_dims % 2 || rot_dims > dk || (rot_dims && !inv_freq))
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    if (dtype == MV_DT_BF16)
+        mv_launch(qkv_prepare_wide_kernel<__nv_bfloat16>, N, 128, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+                  positions, seq_of, page_table, table_stride, page_shift, (__nv_bfloat16*)pool, page_stride,
+                  (__nv_bfloat16*)q_out, nh, nkv, dk, dv);
+    else
+        mv_launch(qkv_prepare_wide_kernel<float>, N, 128, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+                  positions, seq_of, page_table, table_stride, page_shift, (float*)pool, page_stride, (float*)q_out, nh,
+                  nkv, dk, dv);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------ attention
+// One warp per (token, query head).  The keys a query reads are the kept first ones [0, keep) and
+// the window [lo, pos], walked as one run of 32 at a time: each lane scores one key, the warp agrees
+// on the running maximum, then the lanes split the value's elements for the weighted sum.  The sink
+// starts the running maximum and the denominator (its own term is exp(sink - max)), so it is counted
+// once and needs no key.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(128)
+attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
+                      const int* __restrict__ page_table, int table_stride, int page_shift,
+                      const int* __restrict__ positions, const int* __restrict__ seq_of,
+                      const float* __restrict__ sinks, const float* __restrict__ gate, int ld_gate,
+                      T* __restrict__ o, int N, int nh, int nkv, int dk, int dv, float scale, float cap, int window,
+                      int keep_first) {
+    mv_pdl_begin();
+    __shared__ float qs[4][AS_MAX_DIM];
+    const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long warp = (long long)blockIdx.x * 4 + wib;
+    if (warp >= (long long)N * nh) return;
+    const int n = (int)(warp / nh), h = (int)(warp - (long long)n * nh);
+    const int g = h / (nh / nkv);
+    const int pos = positions[n];
+    const int page_size = 1 << page_shift;
+    const int* table = page_table + (size_t)seq_of[n] * table_stride;
+    const size_t v_base = (size_t)nkv * page_size * dk;
+
+    const T* qrow = q + ((size_t)n * nh + h) * dk;
+    for (int d = lane; d < dk; d += 32) qs[wib][d] = mv_to_f32(qrow[d]);
+    __syncwarp();
+
+    float acc[AS_MAX_DIM / 32];
+#pragma unroll
+    for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] = 0.f;
+    float m = sinks ? sinks[h] : -INFINITY;
+    float l = sinks ? 1.f : 0.f;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int keep = min(keep_first, lo);
+    const int total = keep + (pos - lo + 1);
+    const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
+
+    for (int u0 = 0; u0 < total; u0 += 32) {
+        const int u = u0 + lane;
+        const bool valid = u < total;
+        const int t = u < keep ? u : lo + (u - keep);
+        float s = -INFINITY;
+        unsigned long long vaddr = 0;
+        if (valid) {
+            const int page = mv_read_page(table[t >> page_shift]);
+            const T* pbase = pool + (size_t)page * page_stride;
+            const size_t r = (size_t)g * page_size + (t & (page_size - 1));
+            const T* krow = pbase + r * dk;
+            vaddr = (unsigned long long)(pbase + v_base + r * dv);
+            float dot = 0.f;
+            if (VEC) {
+                for (int d = 0; d < dk; d += 8) {
+                    float kv[8];
+                    mv_load8(krow + d, kv);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[wib][d + e], kv[e], dot);
+                }
+            } else {
+                for (int d = 0; d < dk; ++d) dot = fmaf(qs[wib][d], mv_to_f32(krow[d]), dot);
+            }
+            s = dot * scale;
+            if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+        }
+        const float m_new = fmaxf(m, mv_warp_max(s));
+        const float p = valid ? expf(s - m_new) : 0.f;
+        const float corr = expf(m - m_new);          // 0 on the first run when there is no sink (m = -inf)
+        l = l * corr + mv_warp_sum(p);
+#pragma unroll
+        for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] *= corr;
+        m = m_new;
+        const int cnt = min(32, total - u0);
+        for (int j = 0; j < cnt; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const T* vrow = (const T*)__shfl_sync(0xffffffffu, vaddr, j);
+#pragma unroll
+            for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
+                const int d = lane + 32 * r;
+                if (d < dv) acc[r] = fmaf(pj, mv_to_f32(vrow[d]), acc[r]);
+            }
+        }
+    }
+    float mul = 1.0f / l;
+    if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h]));
+    T* orow = o + ((size_t)n * nh + h) * dv;
+#pragma unroll
+    for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
+        const int d = lane + 32 * r;
+        if (d < dv) orow[d] = mv_from_f32<T>(acc[r] * mul);
+    }
+}
+
+// q [N, nh * dk]; o [N, nh * dv]; sinks [nh] or null; gate: 32-bit logits, gate[n * ld_gate + h], or null.
+MV_API int mv_attention_sink(const void* q, const void* pool, long long page_stride, const int* page_table,
+                             int table_stride, int page_size, const int* positions, const int* seq_of,
+                             const float* sinks, const float* gate, int ld_gate, void* o, int dtype, int N, int nh,
+                             int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
+                             cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (dk < 1 || dk > AS_MAX_DIM || dv < 1 || dv > AS_MAX_DIM || nkv < 1 || nh % nkv || (page_size & (page_size - 1)))
+        return (int)cudaErrorInvalidValue;
+    int page_shift = 0;
+    while ((1 << page_shift) < page_size) ++page_shift;
+    const unsigned blocks = (unsigned)(((long long)N * nh + 3) / 4);
+    const int esize = dtype == MV_DT_BF16 ? 2 : 4;
+    const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;
+#define AS_LAUNCH(T, V)                                                                                              \
+    mv_launch(attention_sink_kernel<T, V>, blocks, 128, 0, stream, (const T*)q, (const T*)pool, page_stride,          \
+              page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N, nh, nkv, dk,  \
+              dv, scale, cap, window, keep_first)
+    if (dtype == MV_DT_BF16) {
+        if (vec) AS_LAUNCH(__nv_bfloat16, true); else AS_LAUNCH(__nv_bfloat16, false);
+    } else {
+        if (vec) AS_LAUNCH(float, true); else AS_LAUNCH(float, false);
+    }
+#undef AS_LAUNCH
+    return mv_launch_status();
+}

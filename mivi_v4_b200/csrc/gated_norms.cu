@@ -1,0 +1,188 @@
+// Row-wise pieces that sit between matrix products: a layer norm without bias, a root-mean-square
+// norm over groups of a row followed by a gate, a root-mean-square norm whose result is added to
+// the residual stream, a clamped gated activation, a gate by a per-token table row, and the
+// rounding of 32-bit rows to the model's dtype.  Statistics and activations are 32-bit whatever
+// the output type.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- layer norm
+// y[i, :] = (x[r, :] - mean) / sqrt(mean((x - mean)^2) + eps) * w, r = rows ? rows[i] : i.  Two passes
+// over the row for the statistics (the variance is the mean of the squared deviations).
+template <typename TO>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TO* __restrict__ y,
+                                 const int* __restrict__ rows, int H, float eps) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    const float* xr = x + (size_t)r * H;
+    float s = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) s += xr[h];
+    const float mean = mv_block_sum(s, scratch) / (float)H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float d = xr[h] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+    TO* yr = y + (size_t)i * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) yr[h] = mv_from_f32<TO>((xr[h] - mean) * scale * w[h]);
+}
+
+MV_API int mv_layernorm(const float* x, const float* w, void* y, int y_dtype, const int* rows, int n_rows, int H,
+                        float eps, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (y_dtype == MV_DT_BF16)
+        mv_launch(layernorm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, x, w, (__nv_bfloat16*)y, rows, H, eps);
+    else
+        mv_launch(layernorm_kernel<float>, n_rows, threads, 0, stream, x, w, (float*)y, rows, H, eps);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------- grouped rms norm with a gate
+// A row of C values is cut into groups of ``group``; each group is divided by its root mean
+// square (eps inside the root), multiplied by w[c mod w_len] and by act(gate[n, c]) with act =
+// silu (0) or sigmoid (1).  One warp per (row, group).  The gate has its own row stride.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gate, int ld_gate,
+                     const float* __restrict__ w, int w_len, TO* __restrict__ y, long long n_groups, int C, int group,
+                     float eps, int act) {
+    mv_pdl_begin();
+    const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (wid >= n_groups) return;
+    const int per_row = C / group;
+    const long long n = wid / per_row;
+    const int c0 = (int)(wid - n * per_row) * group;
+    const float* xr = x + (size_t)n * C + c0;
+    float ss = 0.f;
+    for (int d = lane; d < group; d += 32) ss = fmaf(xr[d], xr[d], ss);
+    ss = mv_warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / (float)group + eps);
+    const float* gr = gate + (size_t)n * ld_gate + c0;
+    TO* yr = y + (size_t)n * C + c0;
+    for (int d = lane; d < group; d += 32) {
+        const float g = gr[d];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        yr[d] = mv_from_f32<TO>(xr[d] * scale * w[(c0 + d) % w_len] * (act == 0 ? g * sg : sg));
+    }
+}
+
+MV_API int mv_gated_rmsnorm(const float* x, const float* gate, int ld_gate, const float* w, int w_len, void* y,
+                            int y_dtype, int N, int C, int group, float eps, int act, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (group < 1 || C % group || w_len < 1) return (int)cudaErrorInvalidValue;
+    const long long n_groups = (long long)N * (C / group);
+    const unsigned blocks = (unsigned)((n_groups + 7) / 8);
+    if (y_dtype == MV_DT_BF16)
+        mv_launch(gated_rmsnorm_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, gate, ld_gate, w, w_len,
+                  (__nv_bfloat16*)y, n_groups, C, group, eps, act);
+    else
+        mv_launch(gated_rmsnorm_kernel<float>, blocks, 256, 0, stream, x, gate, ld_gate, w, w_len, (float*)y, n_groups,
+                  C, group, eps, act);
+    return mv_launch_status();
+}
+
+// ----------------------------------------------- rms norm added to the residual stream
+// resid[n, :] += y[n, :] / sqrt(mean(y[n, :]^2) + eps) * w
+__global__ void rmsnorm_add_kernel(const float* __restrict__ y, const float* __restrict__ w, float* __restrict__ resid,
+                                   int H, float eps) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const float* yr = y + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) ss = fmaf(yr[h], yr[h], ss);
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+    float* rr = resid + (size_t)blockIdx.x * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) rr[h] += yr[h] * scale * w[h];
+}
+
+MV_API int mv_rmsnorm_add(const float* y, const float* w, float* resid, int N, int H, float eps, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    mv_launch(rmsnorm_add_kernel, N, threads, 0, stream, y, w, resid, H, eps);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------ clamped gated activation
+// h[n, f] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
+// gate = gu[n, f], up = gu[n, F + f].
+template <typename TO>
+__global__ void glu_clamped_kernel(const float* __restrict__ gu, TO* __restrict__ h, long long total, int F, float limit,
+                                   float alpha) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / F;
+    const int f = (int)(i - n * F);
+    const float g = fminf(gu[n * 2 * F + f], limit);
+    const float u = fminf(fmaxf(gu[n * 2 * F + F + f], -limit), limit);
+    h[i] = mv_from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+}
+
+MV_API int mv_glu_clamped(const float* gu, void* h, int h_dtype, int N, int F, float limit, float alpha,
+                          cudaStream_t stream) {
+    const long long total = (long long)N * F;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (h_dtype == MV_DT_BF16)
+        mv_launch(glu_clamped_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gu, (__nv_bfloat16*)h, total, F, limit, alpha);
+    else
+        mv_launch(glu_clamped_kernel<float>, blocks, 256, 0, stream, gu, (float*)h, total, F, limit, alpha);
+    return mv_launch_status();
+}
+
+// --------------------------------------------------- gate by a row of a token table
+// out[n, d] = gelu_tanh(p[n, d]) * table[tokens[n], col0 + d], d < D; the table's rows have ld_table elements.
+template <typename TT, typename TO>
+__global__ void table_gate_kernel(const float* __restrict__ p, const TT* __restrict__ table, int ld_table, int col0,
+                                  const int* __restrict__ tokens, TO* __restrict__ out, long long total, int D) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const long long n = i / D;
+    const int d = (int)(i - n * D);
+    const float zv = p[i];
+    const float gelu = 0.5f * zv * (1.0f + tanhf(0.7978845608028654f * (zv + 0.044715f * zv * zv * zv)));
+    out[i] = mv_from_f32<TO>(gelu * mv_to_f32(table[(size_t)tokens[n] * ld_table + col0 + d]));
+}
+
+MV_API int mv_table_gate(const float* p, const void* table, int table_dtype, int ld_table, int col0, const int* tokens,
+                         void* out, int out_dtype, int N, int D, cudaStream_t stream) {
+    const long long total = (long long)N * D;
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (table_dtype == MV_DT_BF16 && out_dtype == MV_DT_BF16)
+        mv_launch(table_gate_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, 256, 0, stream, p, (const __nv_bfloat16*)table,
+                  ld_table, col0, tokens, (__nv_bfloat16*)out, total, D);
+    else if (table_dtype == MV_DT_F32 && out_dtype == MV_DT_F32)
+        mv_launch(table_gate_kernel<float, float>, blocks, 256, 0, stream, p, (const float*)table, ld_table, col0, tokens,
+                  (float*)out, total, D);
+    else if (table_dtype == MV_DT_F32)
+        mv_launch(table_gate_kernel<float, __nv_bfloat16>, blocks, 256, 0, stream, p, (const float*)table, ld_table, col0,
+                  tokens, (__nv_bfloat16*)out, total, D);
+    else
+        return (int)cudaErrorInvalidValue;
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------- rounding
+// out = x rounded to the output type (the residual stream as a product's operand)
+template <typename TO>
+__global__ void round_rows_kernel(const float* __restrict__ x, TO* __restrict__ out, long long total) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) out[i] = mv_from_f32<TO>(x[i]);
+}
+
+MV_API int mv_round_rows(const float* x, void* out, int out_dtype, long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (out_dtype == MV_DT_BF16)
+        mv_launch(round_rows_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, (__nv_bfloat16*)out, total);
+    else
+        mv_launch(round_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)out, total);
+    return mv_launch_status();
+}

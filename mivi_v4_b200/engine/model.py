@@ -63,7 +63,7 @@ class Model:
         out: Dict[str, ParamSpec] = {}
         for p in self.parts():
             for name, spec in p.named_param_specs().items():
-                if name in out:
+                if name in out and (out[name] != spec or name not in p.shared_names()):
                     raise ValueError(f"two parts claim the tensor {name!r}")
                 out[name] = spec
         return out

@@ -45,6 +45,16 @@ _SIGNATURES = {
         "mv_attention_generic": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_decode": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _I, _I,
                                 _I, _I, _P],
+        "mv_layernorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
+        "mv_gated_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
+        "mv_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _P],
+        "mv_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
+        "mv_table_gate": [_P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+        "mv_round_rows": [_P, _P, _I, _Q, _P],
+        "mv_decay_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _F, _F, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _P],
+        "mv_attention_sink": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I,
+                              _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
@@ -328,6 +338,213 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
         _need(out, "rmsnorm out", None, (n, H)), _dt(out),
         _need(rows, "rmsnorm rows", torch.int32, optional=True), n, H, float(eps), _stream()), "mv_rmsnorm")
     account(n * H * (4 + out.element_size()))
+    return out
+
+
+def layernorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+              rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[i] = (x[r] - mean) / sqrt(var + eps) * w with r = rows[i] or i; no bias; statistics in float32,
+    the variance being the mean of the squared deviations."""
+    H = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    _check(_fn("core", "mv_layernorm")(
+        _need(x, "layernorm x", torch.float32), _need(w, "layernorm weight", torch.float32, (H,)),
+        _need(out, "layernorm out", None, (n, H)), _dt(out),
+        _need(rows, "layernorm rows", torch.int32, optional=True), n, H, float(eps), _stream()), "mv_layernorm")
+    account(n * H * (4 + out.element_size()))
+    return out
+
+
+GATE_SILU, GATE_SIGMOID = 0, 1
+
+
+def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group: int, eps: float, act: int,
+                  out: torch.Tensor) -> torch.Tensor:
+    """Every group of ``group`` consecutive values of a row of x [N, C] (float32) is divided by its root mean
+    square, multiplied by w[c mod len(w)] and by act(gate[n, c]): ``GATE_SILU`` or ``GATE_SIGMOID``.  ``gate``
+    (float32) may be a column slice of a wider matrix: only its rows must be contiguous."""
+    N, C = x.shape
+    if group < 1 or C % group:
+        raise KernelError(f"gated_rmsnorm: rows of {C} values do not split into groups of {group}")
+    if w.numel() not in (group, C):
+        raise KernelError(f"gated_rmsnorm: {w.numel()} weights for groups of {group} in rows of {C}")
+    if (not gate.is_cuda or gate.dtype != torch.float32 or gate.dim() != 2 or tuple(gate.shape) != (N, C)
+            or gate.stride(1) != 1):
+        raise KernelError(f"gated_rmsnorm: gate must be float32 [{N}, {C}] with unit column stride, got "
+                          f"{gate.dtype} {tuple(gate.shape)} strides {gate.stride()}")
+    _check(_fn("core", "mv_gated_rmsnorm")(
+        _need(x, "gated_rmsnorm x", torch.float32), gate.data_ptr(), gate.stride(0),
+        _need(w, "gated_rmsnorm weight", torch.float32), w.numel(), _need(out, "gated_rmsnorm out", None, (N, C)),
+        _dt(out), N, C, int(group), float(eps), int(act), _stream()), "mv_gated_rmsnorm")
+    account(N * C * (8 + out.element_size()))
+    return out
+
+
+def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.Tensor) -> torch.Tensor:
+    """resid += y / sqrt(mean(y^2) + eps) * w, row by row, all float32."""
+    N, H = y.shape
+    _check(_fn("core", "mv_rmsnorm_add")(
+        _need(y, "rmsnorm_add y", torch.float32), _need(w, "rmsnorm_add weight", torch.float32, (H,)),
+        _need(resid, "residual stream", torch.float32, (N, H)), N, H, float(eps), _stream()), "mv_rmsnorm_add")
+    account(N * H * 12)
+    return resid
+
+
+def glu_clamped(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """out = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit); gate and
+    up are the two halves of a row of ``gu`` (float32)."""
+    N, F2 = gu.shape
+    F = F2 // 2
+    _check(_fn("core", "mv_glu_clamped")(
+        _need(gu, "glu in", torch.float32, (N, 2 * F)), _need(out, "glu out", None, (N, F)), _dt(out), N, F,
+        float(limit), float(alpha), _stream()), "mv_glu_clamped")
+    account(_nbytes(gu, out))
+    return out
+
+
+def table_gate(p: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[n, d] = gelu_tanh(p[n, d]) * table[tokens[n], col0 + d]: a projection gated by a slice of a
+    per-token table row."""
+    N, D = p.shape
+    if table.dim() != 2 or col0 < 0 or col0 + D > table.shape[1]:
+        raise KernelError(f"table_gate: columns {col0}..{col0 + D} are outside a table of {tuple(table.shape)}")
+    if _dt(table) == BF16 and _dt(out) != BF16:
+        raise KernelError("table_gate: a bfloat16 table needs a bfloat16 output")
+    _check(_fn("core", "mv_table_gate")(
+        _need(p, "table_gate p", torch.float32), _need(table, "table_gate table"), _dt(table), table.shape[1],
+        int(col0), _need(tokens, "tokens", torch.int32), _need(out, "table_gate out", None, (N, D)), _dt(out), N, D,
+        _stream()), "mv_table_gate")
+    account(_nbytes(p, out) + N * D * table.element_size())
+    return out
+
+
+def round_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x (float32) rounded to out's dtype."""
+    _check(_fn("core", "mv_round_rows")(
+        _need(x, "round_rows x", torch.float32), _need(out, "round_rows out", None, tuple(x.shape)), _dt(out),
+        x.numel(), _stream()), "mv_round_rows")
+    account(_nbytes(x, out))
+    return out
+
+
+MAX_SCAN_KEY_DIM = 256
+SCAN_ACT_NONE, SCAN_ACT_SILU = 0, 1
+
+
+def _cols(t: torch.Tensor, name: str, n_rows: int, width: int):
+    """Pointer and row stride of a float32 matrix that may be a column slice of a wider one."""
+    if (not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.shape[0] != n_rows or t.shape[1] != width
+            or (t.stride(1) != 1 and width > 1)):
+        raise KernelError(f"{name}: needs float32 [{n_rows}, {width}] on a CUDA device with unit column stride, got "
+                          f"{t.dtype} {tuple(t.shape)} strides {t.stride()} on {t.device}")
+    return t.data_ptr(), t.stride(0)
+
+
+def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+               cu: torch.Tensor, out: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int, *,
+               decay_logits: Optional[torch.Tensor] = None, inv_tau: float = 1.0,
+               head_decay: Optional[torch.Tensor] = None, q_scale: float = 1.0, act: int = SCAN_ACT_NONE) -> torch.Tensor:
+    """Linear attention with a decaying state, per head: S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t, over the
+    step's tokens in order, from and into ``state`` [slots, heads, dv, dk] (float32, transposed: a value
+    column's key channels lie together).  The decay a_t is sigmoid(decay_logits)^inv_tau per token and key
+    channel, or ``head_decay`` [heads], a constant per head.  q, k [N, heads * dk] and v [N, heads * dv] are
+    float32 and may be column slices of one wider matrix; ``act`` is applied to all three as they are read
+    and ``q_scale`` multiplies q.  Everything is computed in float32."""
+    N = out.shape[0]
+    if not 1 <= dk <= MAX_SCAN_KEY_DIM:
+        raise KernelError(f"decay_scan: key size {dk} is outside 1..{MAX_SCAN_KEY_DIM}")
+    if (decay_logits is None) == (head_decay is None):
+        raise KernelError("decay_scan: give either decay logits per token and channel or a decay per head")
+    qp, ldq = _cols(q, "decay_scan q", N, n_heads * dk)
+    kp, ldk = _cols(k, "decay_scan k", N, n_heads * dk)
+    vp, ldv = _cols(v, "decay_scan v", N, n_heads * dv)
+    zp, ldz = _cols(decay_logits, "decay_scan decay logits", N, n_heads * dk) if decay_logits is not None else (None, 0)
+    _need(state, "decay_scan state", torch.float32, (None, n_heads, dv, dk))
+    _guard("core", "decay_scan", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_decay_scan")(
+        qp, ldq, kp, ldk, vp, ldv, zp, ldz, _need(head_decay, "head decay", torch.float32, (n_heads,), True),
+        float(inv_tau), float(q_scale), int(act), state.data_ptr(), _need(slots, "slots", torch.int32),
+        _need(cu, "cu", torch.int32), _need(out, "decay_scan out", torch.float32, (N, n_heads * dv)), int(n_seqs),
+        n_heads, dk, dv, _stream()), "mv_decay_scan")
+    account(N * n_heads * (2 * dk + 2 * dv) * 4 + 2 * n_seqs * n_heads * dk * dv * 4, 4 * N * n_heads * dk * dv)
+    return out
+
+
+def kv_page_elems(nkv: int, page_size: int, dk: int, dv: int) -> int:
+    """Elements of one layer's page when keys and values differ in size: [kv head][row][dk] keys, then
+    [kv head][row][dv] values."""
+    return nkv * page_size * (dk + dv)
+
+
+def _check_kv_wide(pool: torch.Tensor, nkv: int, page_size: int, dk: int, dv: int, what: str) -> None:
+    if dk == dv and pool.dim() == 5:
+        _check_kv(pool, nkv, dk, page_size, what)
+        return
+    if pool.dim() != 2 or pool.shape[1] != kv_page_elems(nkv, page_size, dk, dv):
+        raise KernelError(f"{what}: cache pool shape {tuple(pool.shape)}, expected [pages, "
+                          f"{kv_page_elems(nkv, page_size, dk, dv)}] ({nkv} kv heads x {page_size} rows x ({dk} + {dv}))")
+    if page_size & (page_size - 1):
+        raise KernelError(f"{what}: page size {page_size} is not a power of two")
+
+
+def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
+                     rot_dims: int, inv_freq: Optional[torch.Tensor], positions, seq_of, page_table,
+                     pool: torch.Tensor, page_size: int, q_out: torch.Tensor, nh: int, nkv: int, dk: int,
+                     dv: int) -> torch.Tensor:
+    """From a row [q | k | v | ...] of a fused projection (float32, any row stride): root-mean-square norm over
+    the whole of q and the whole of k (weights wq [nh * dk], wk [nkv * dk]; None: no norm), rotation of the
+    first ``rot_dims`` elements of every head (element i with i + rot_dims / 2, angle pos * inv_freq[i]), q
+    out in the model's dtype, k and v into the token's row of its page."""
+    N = q_out.shape[0]
+    need = nh * dk + nkv * (dk + dv)
+    if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[0] != N or proj.shape[1] < need
+            or proj.stride(1) != 1):
+        raise KernelError(f"qkv_prepare_wide: projection must be float32 [{N}, >= {need}], got {proj.dtype} "
+                          f"{tuple(proj.shape)}")
+    if rot_dims % 2 or not 0 <= rot_dims <= dk:
+        raise KernelError(f"qkv_prepare_wide: {rot_dims} rotated elements in heads of {dk}")
+    _check_kv_wide(pool, nkv, page_size, dk, dv, "qkv_prepare_wide")
+    if pool.dtype != q_out.dtype:
+        raise KernelError(f"qkv_prepare_wide: cache is {pool.dtype} but q is {q_out.dtype}")
+    _guard("core", "attention_sink", proj.device, n_pages=pool.shape[0])
+    _check(_fn("core", "mv_qkv_prepare_wide")(
+        proj.data_ptr(), proj.stride(0), _need(wq, "q norm weight", torch.float32, (nh * dk,), True),
+        _need(wk, "k norm weight", torch.float32, (nkv * dk,), True), float(eps), int(rot_dims),
+        _need(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,), rot_dims == 0),
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size, _need(pool, "cache pool"),
+        pool.stride(0), _need(q_out, "q out", None, (N, nh * dk)), _dt(q_out), N, nh, nkv, dk, dv, _stream()),
+        "mv_qkv_prepare_wide")
+    account(N * need * 4 + N * (nh * dk + nkv * (dk + dv)) * q_out.element_size())
+    return q_out
+
+
+def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
+                   out: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, scale: float, *, softcap: float = 0.0,
+                   window: int = 0, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
+                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal softmax attention of every token of the step over its sequence's cache (which already holds the
+    step's own keys), keys of size dk and values of size dv.  ``softcap`` c > 0: s <- c tanh(s / c).  ``window``
+    w > 0 with ``keep_first`` f: query i reads key j if i - j < w or j < f.  ``sinks`` [nh]: exp(sink) joins
+    each head's denominator.  ``gate``: float32 logits [N, nh] (a column slice is fine); the head's output is
+    multiplied by sigmoid(gate)."""
+    N = q.shape[0]
+    if not (1 <= dk <= MAX_HEAD_DIM and 1 <= dv <= MAX_HEAD_DIM):
+        raise KernelError(f"attention_sink: key size {dk} and value size {dv} must lie in 1..{MAX_HEAD_DIM}")
+    if nkv < 1 or nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    _check_kv_wide(pool, nkv, page_size, dk, dv, "attention_sink")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    gp, ldg = _cols(gate, "attention gate", N, nh) if gate is not None else (None, 0)
+    _guard("core", "attention_sink", q.device, n_pages=pool.shape[0])
+    _check(_fn("core", "mv_attention_sink")(
+        _need(q, "q", None, (N, nh * dk)), _need(pool, "cache pool"), pool.stride(0),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
+        _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
+        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
+        _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), _stream()),
+        "mv_attention_sink")
     return out
 
 

@@ -10,6 +10,7 @@ mixer         cache_need() -> KVNeed | StateNeed | None | a list of those
               forward(u[N, hidden], resid, step, cache_view) -> None   (a list of views for a list of needs)
 feed_forward  forward(g[N, hidden], resid, step) -> None; one that overrides cache_need() is also passed
               view=<its view or list of views>
+token_input   forward(resid, step) -> None: a per-layer input that depends on the token ids
 block         cache_need(); forward(resid, step, cache_view) -> None
 embedding     forward(step) -> resid f32[N, hidden]
 head          forward(f[n, hidden], step, embedding) -> logits f32[n, vocab]
@@ -24,6 +25,7 @@ from .spec import ParamSpec
 class Part:
     kind = "?"
     prefix = ""
+    names: Dict[str, str] = {}          # local tensor name -> checkpoint name where that is not prefix + local name
     nested_roles: Dict[str, str] = {}
     # False for a part whose forward reads device values on the host or launches work that depends
     # on the step's host-side lists: a model with such a part runs its decode steps launch by launch
@@ -54,8 +56,16 @@ class Part:
     def nested(self) -> Dict[str, "Part"]:
         return {}
 
+    def shared_names(self) -> set:
+        """Checkpoint names among this part's tensors (nested parts included) that other parts may claim as
+        well: the ones given in full through ``names``."""
+        out = set(self.names.values())
+        for sub in self.nested().values():
+            out |= sub.shared_names()
+        return out
+
     def named_param_specs(self) -> Dict[str, ParamSpec]:
-        out = {self.prefix + k: v for k, v in self.param_specs().items()}
+        out = {self.names.get(k, self.prefix + k): v for k, v in self.param_specs().items()}
         for sub in self.nested().values():
             out.update(sub.named_param_specs())
         return out
@@ -67,7 +77,7 @@ class Part:
             setattr(self, k.replace(".", "_"), v)
 
     def load_named(self, named: Dict[str, "object"]) -> None:
-        mine = {k: named[self.prefix + k] for k in self.param_specs()}
+        mine = {k: named[self.names.get(k, self.prefix + k)] for k in self.param_specs()}
         self.load(mine)
         for sub in self.nested().values():
             sub.load_named(named)

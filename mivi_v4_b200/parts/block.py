@@ -81,3 +81,43 @@ class PreNormBlock(Part):
         with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
             self.ffn.forward(g, resid, step, **kw)
         step.leave_link(leave)
+
+
+@register("block", "prenorm_optional")
+class PreNormOptionalBlock(Part):
+    """x += mixer(norm(x)); then, if the layer has a feed-forward, x += feed_forward(norm(x)); then, if it has
+    a per-layer token input, that adds to x.  The residual stream stays in float32; the normed activations
+    are in the model's dtype.  Norms are kernels of their own here (no product carries them)."""
+
+    nested_roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "feed_forward",
+                    "token_input": "token_input"}
+
+    def __init__(self, mixer_norm, mixer, ffn_norm=None, ffn=None, token_input=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.token_input = mixer_norm, mixer, ffn_norm, ffn, token_input
+
+    def nested(self):
+        parts = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "ffn_norm": self.ffn_norm, "ffn": self.ffn,
+                 "token_input": self.token_input}
+        return {k: v for k, v in parts.items() if v is not None}
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def forward(self, resid, step, view) -> None:
+        N, H = resid.shape
+        u = self.scratch(step, "normed", (N, H), step.dtype)
+        with profile_stage("norm"):
+            self.mixer_norm.forward(resid, u)
+        with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
+            self.mixer.forward(u, resid, step, view)
+        if self.ffn is not None:
+            g = self.scratch(step, "normed", (N, H), step.dtype)
+            with profile_stage("norm"):
+                self.ffn_norm.forward(resid, g)
+            with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
+                self.ffn.forward(g, resid, step)
+        if self.token_input is not None:
+            with profile_stage("token_input " + getattr(self.token_input, "kind", "?")):
+                self.token_input.forward(resid, step)

@@ -55,3 +55,33 @@ class SwiGLU(Part):
             linear(g, self.w13, gu, scale=scale)
             K.swiglu(gu, h, self.group)
         linear(h, self.w2, resid, accumulate=True, emit=emit)
+
+
+@register("feed_forward", "clamped_glu")
+class ClampedGLU(Part):
+    """x + (g * sigmoid(alpha g) * (u + 1)) W_down^T with g = min(h W_gate^T, limit) and
+    u = clamp(h W_up^T, -limit, limit); no biases.  ``alpha`` is the constant of the sigmoid approximation of
+    gelu (1.702).  Gate and up are one product (the two matrices end to end); the activation is computed in
+    float32 from its float32 results."""
+
+    def __init__(self, hidden: int, ff: int, limit: float, alpha: float = 1.702):
+        self.hidden, self.ff, self.limit, self.alpha = int(hidden), int(ff), float(limit), float(alpha)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, F = self.hidden, self.ff
+        return {"gate": ParamSpec((F, H)), "up": ParamSpec((F, H)), "down": ParamSpec((H, F))}
+
+    def load(self, t) -> None:
+        wg, wu = t["gate"], t["up"]
+        if wg.dtype != wu.dtype:
+            wg, wu = wg.float(), wu.float()
+        self.w_gu = torch.cat([wg, wu], dim=0).contiguous()
+        self.w_down = t["down"]
+
+    def forward(self, g, resid, step) -> None:
+        N = g.shape[0]
+        gu = self.scratch(step, "proj", (N, 2 * self.ff), torch.float32)
+        linear(g, self.w_gu, gu)
+        h = self.scratch(step, "ffh", (N, self.ff), step.dtype)
+        K.glu_clamped(gu, h, self.limit, self.alpha)
+        linear(h, self.w_down, resid, accumulate=True)

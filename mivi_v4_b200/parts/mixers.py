@@ -11,6 +11,7 @@ from ..ops import kernels as K
 from ..ops.linear import (conv_rows_grouped, heads_fused_ok, linear, linear_heads, linear_shortconv_decode, norm_link_ok,
                           shortconv_decode_fused_ok)
 from .base import Part
+from .position import Rope
 from .registry import register
 from .spec import ParamSpec
 
@@ -183,3 +184,192 @@ class GroupedQueryAttention(Part):
             K.account(2 * nkv * hd * view.pool.element_size() * rows + 2 * N * nh * hd * q.element_size(),
                       4 * nh * hd * pairs)
         linear(o, self.w_o, resid, accumulate=True, emit=emit)
+
+
+def _fuse_rows(mats, multiple: int = 16) -> torch.Tensor:
+    """Several projections of the same input as one matrix, their rows end to end, padded with zero rows to
+    a multiple of ``multiple`` (the padding's results are never read)."""
+    if len({m.dtype for m in mats}) != 1:
+        mats = [m.float() for m in mats]
+    rows = sum(m.shape[0] for m in mats)
+    pad = -rows % multiple
+    if pad:
+        mats = list(mats) + [torch.zeros((pad, mats[0].shape[1]), dtype=mats[0].dtype, device=mats[0].device)]
+    return torch.cat(mats, dim=0).contiguous()
+
+
+@register("mixer", "gated_linear_attention")
+class GatedLinearAttention(Part):
+    """Linear attention with a matrix state per head and a learned decay per key channel:
+    q = W_q h / sqrt(dk), k = W_k h, v = W_v h; a = sigmoid(W_a2 (W_a1 h) + b)^(1/tau);
+    S <- diag(a) S + k v^T, o = S^T q; each head's o is divided by its root mean square and multiplied by
+    ``norm`` [dv] (one weight for all heads), then by silu(W_g h); W_o maps the heads back.  The state
+    [heads, dv, dk] is float32 per sequence and starts at zero; decay, state and sums are float32 in every
+    run.  ``rank`` is the inner size of the decay's two-step projection; None takes it from the checkpoint."""
+
+    def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, tau: float, eps: float,
+                 rank: Optional[int] = None):
+        if not 1 <= key_dim <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"key size {key_dim} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        if tau <= 0:
+            raise ValueError(f"tau must be positive, got {tau}")
+        self.hidden, self.nh, self.dk, self.dv = int(hidden), int(n_heads), int(key_dim), int(value_dim)
+        self.tau, self.eps, self.rank = float(tau), float(eps), None if rank is None else int(rank)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, qk, vv, r = self.hidden, self.nh * self.dk, self.nh * self.dv, self.rank
+        return {"q": ParamSpec((qk, H)), "k": ParamSpec((qk, H)), "v": ParamSpec((vv, H)), "g": ParamSpec((vv, H)),
+                "o": ParamSpec((H, vv)), "norm": ParamSpec((self.dv,), "vector", "norm"),
+                "a1": ParamSpec((r, H)), "a2": ParamSpec((qk, r)), "a2.b": ParamSpec((qk,), "vector", "bias")}
+
+    def load(self, t) -> None:
+        if t["a1"].shape[0] != t["a2"].shape[1]:
+            raise ValueError(f"the decay's two projections disagree: a1 is {tuple(t['a1'].shape)}, a2 {tuple(t['a2'].shape)}")
+        self.w_qkvg = _fuse_rows([t["q"], t["k"], t["v"], t["g"]])
+        self.w_a1, self.w_a2, self.b_a2 = t["a1"], t["a2"], t["a2.b"]
+        self.w_o, self.norm = t["o"], t["norm"]
+
+    def cache_need(self):
+        return StateNeed((self.nh, self.dv, self.dk))
+
+    def forward(self, u, resid, step, view) -> None:
+        N = u.shape[0]
+        qk, vv = self.nh * self.dk, self.nh * self.dv
+        proj = self.scratch(step, "proj", (N, self.w_qkvg.shape[0]), torch.float32)
+        linear(u, self.w_qkvg, proj)
+        low = self.scratch(step, "low", (N, self.w_a1.shape[0]), step.dtype)
+        linear(u, self.w_a1, low)
+        z = self.scratch(step, "z", (N, qk), torch.float32)
+        linear(low, self.w_a2, z, bias=self.b_a2)
+        o = self.scratch(step, "o", (N, vv), torch.float32)
+        K.decay_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], view.state, step.slots, step.cu, o,
+                     step.n_seqs, self.nh, self.dk, self.dv, decay_logits=z, inv_tau=1.0 / self.tau,
+                     q_scale=self.dk ** -0.5)
+        y = self.scratch(step, "mix", (N, vv), step.dtype)
+        K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.dv, self.eps, K.GATE_SILU, y)
+        linear(y, self.w_o, resid, accumulate=True)
+
+
+@register("mixer", "lightning_attention")
+class LightningAttention(Part):
+    """Linear attention with a matrix state per head and one fixed decay per head:
+    q = silu(W_q h), k = silu(W_k h), v = silu(W_v h); S <- decay_h S + k v^T, o = S^T q; the heads together
+    are divided by their root mean square and multiplied by ``norm`` [heads * dv], then by sigmoid(W_g h);
+    W_o maps them back.  The state [heads, dv, dk] is float32 per sequence and starts at zero."""
+
+    def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, decay, eps: float):
+        decay = [float(d) for d in decay]
+        if len(decay) != int(n_heads):
+            raise ValueError(f"{len(decay)} decays for {n_heads} heads")
+        if not 1 <= key_dim <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"key size {key_dim} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        self.hidden, self.nh, self.dk, self.dv = int(hidden), int(n_heads), int(key_dim), int(value_dim)
+        self.decay, self.eps = decay, float(eps)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, qk, vv = self.hidden, self.nh * self.dk, self.nh * self.dv
+        return {"q": ParamSpec((qk, H)), "k": ParamSpec((qk, H)), "v": ParamSpec((vv, H)), "g": ParamSpec((vv, H)),
+                "o": ParamSpec((H, vv)), "norm": ParamSpec((vv,), "vector", "norm")}
+
+    def load(self, t) -> None:
+        self.w_qkvg = _fuse_rows([t["q"], t["k"], t["v"], t["g"]])
+        self.w_o, self.norm = t["o"], t["norm"]
+        # the decays as float32, rounded once from the configuration's numbers
+        self.decay_t = torch.tensor(self.decay, dtype=torch.float64).to(torch.float32).to(self.w_o.device)
+
+    def cache_need(self):
+        return StateNeed((self.nh, self.dv, self.dk))
+
+    def forward(self, u, resid, step, view) -> None:
+        N = u.shape[0]
+        qk, vv = self.nh * self.dk, self.nh * self.dv
+        proj = self.scratch(step, "proj", (N, self.w_qkvg.shape[0]), torch.float32)
+        linear(u, self.w_qkvg, proj)
+        o = self.scratch(step, "o", (N, vv), torch.float32)
+        K.decay_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], view.state, step.slots, step.cu, o,
+                     step.n_seqs, self.nh, self.dk, self.dv, head_decay=self.decay_t, act=K.SCAN_ACT_SILU)
+        y = self.scratch(step, "mix", (N, vv), step.dtype)
+        K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, vv, self.eps, K.GATE_SIGMOID, y)
+        linear(y, self.w_o, resid, accumulate=True)
+
+
+@register("mixer", "sink_attention")
+class SinkAttention(Part):
+    """Grouped-query softmax attention over the cache with keys of size ``key_dim`` and values of size
+    ``value_dim``: q, k, v projections without bias; a root-mean-square norm over the WHOLE q and the whole
+    k projection (all heads at once; ``qk_norm_eps`` None: none) before the rotation; the position part's
+    rotation of the first ``position.head_dim`` elements of every head, element i paired with
+    i + position.head_dim / 2; scores (q . k) * scale, capped as c tanh(s / c) when ``softcap`` c > 0; a window
+    of ``window`` tokens (0: none) that also keeps the sequence's first ``keep_first`` tokens; with ``sink`` a
+    learned number per head whose exponential joins the softmax's denominator; with ``gated`` each head's
+    output times sigmoid of one projection of the layer's input per head; then the out projection.  Scores
+    and softmax are float32."""
+
+    nested_roles = {"position": "position"}
+
+    def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, scale: float,
+                 position, softcap: float = 0.0, window: int = 0, keep_first: int = 0,
+                 qk_norm_eps: Optional[float] = None, sink: bool = True, gated: bool = True):
+        if n_kv_heads < 1 or n_heads % n_kv_heads:
+            raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+        if not (1 <= key_dim <= K.MAX_HEAD_DIM and 1 <= value_dim <= K.MAX_HEAD_DIM):
+            raise ValueError(f"key size {key_dim} and value size {value_dim} must lie in 1..{K.MAX_HEAD_DIM}")
+        self.hidden, self.nh, self.nkv = int(hidden), int(n_heads), int(n_kv_heads)
+        self.dk, self.dv, self.scale, self.softcap = int(key_dim), int(value_dim), float(scale), float(softcap or 0.0)
+        self.window, self.keep_first = int(window), int(keep_first) if window else 0
+        self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
+        self.sink, self.gated, self.position = bool(sink), bool(gated), position
+        self.rot_dims = 0
+        if isinstance(position, Rope):
+            if position.style != "half_split" or position.head_dim > self.dk:
+                raise ValueError("the rotation pairs element i with i + dims / 2 over at most the key size")
+            self.rot_dims = position.head_dim
+        elif position.rotary("cpu") is not None:
+            raise ValueError("a rotation that is not a Rope part cannot say how many elements it turns")
+
+    def nested(self):
+        return {"position": self.position}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, nh, nkv, dk, dv = self.hidden, self.nh, self.nkv, self.dk, self.dv
+        specs = {"q": ParamSpec((nh * dk, H)), "k": ParamSpec((nkv * dk, H)), "v": ParamSpec((nkv * dv, H)),
+                 "o": ParamSpec((H, nh * dv))}
+        if self.qk_norm_eps is not None:
+            specs["q.norm"] = ParamSpec((nh * dk,), "vector", "norm")
+            specs["k.norm"] = ParamSpec((nkv * dk,), "vector", "norm")
+        if self.sink:
+            specs["sink"] = ParamSpec((nh,), "vector", "bias")
+        if self.gated:
+            specs["g"] = ParamSpec((nh, H))
+        return specs
+
+    def load(self, t) -> None:
+        self.w_qkvg = _fuse_rows([t["q"], t["k"], t["v"]] + ([t["g"]] if self.gated else []))
+        self.w_o = t["o"]
+        self.q_norm, self.k_norm, self.sinks = t.get("q.norm"), t.get("k.norm"), t.get("sink")
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.keep_first)
+
+    def forward(self, u, resid, step, view) -> None:
+        N = u.shape[0]
+        nh, nkv, dk, dv = self.nh, self.nkv, self.dk, self.dv
+        proj = self.scratch(step, "proj", (N, self.w_qkvg.shape[0]), torch.float32)
+        linear(u, self.w_qkvg, proj)
+        rot = self.position.rotary(u.device) if self.rot_dims else None
+        q = self.scratch(step, "q", (N, nh * dk), step.dtype)
+        K.qkv_prepare_wide(proj, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.rot_dims,
+                           rot[0] if rot is not None else None, step.positions, step.seq_of, view.page_table,
+                           view.pool, view.page_size, q, nh, nkv, dk, dv)
+        o = self.scratch(step, "mix", (N, nh * dv), step.dtype)
+        g0 = nh * dk + nkv * (dk + dv)
+        K.attention_sink(q, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o, nh, nkv, dk,
+                         dv, self.scale, softcap=self.softcap, window=self.window, keep_first=self.keep_first,
+                         sinks=self.sinks, gate=proj[:, g0:g0 + nh] if self.gated else None)
+        if K.profiling_on():
+            reach = (self.window + self.keep_first) if self.window else None
+            pairs = sum(sum(min(s + i + 1, reach) if reach else s + i + 1 for i in range(n))
+                        for s, n in zip(step.host_starts, step.host_lens))
+            K.account(nkv * (dk + dv) * view.pool.element_size() * pairs + N * nh * (dk + dv) * q.element_size(),
+                      2 * nh * (dk + dv) * pairs)
+        linear(o, self.w_o, resid, accumulate=True)

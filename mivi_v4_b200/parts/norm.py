@@ -33,3 +33,19 @@ class RMSNorm(Part):
         return K.NormLink(self, self.weight, self.eps, self.dim,
                           step.ws.get("link_rows_" + name, (n, self.dim), torch.bfloat16),
                           step.ws.get("link_sums_" + name, (n, -(-self.dim // 64) * 4), torch.float32))
+
+
+@register("norm", "layernorm")
+class LayerNorm(Part):
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight over the last dimension, no bias, in
+    float32.  It is not carried by the products around it (it has no ``link``): it always runs as a kernel."""
+
+    def __init__(self, dim: int, eps: float):
+        self.dim, self.eps = int(dim), float(eps)
+        self.weight: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((self.dim,), "vector", "norm")}
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return K.layernorm(x, self.weight, self.eps, out, rows)

@@ -7,7 +7,7 @@ from __future__ import annotations
 
 from typing import Callable, Dict
 
-ROLES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head")
+ROLES = ("mixer", "feed_forward", "norm", "position", "block", "embedding", "head", "token_input")
 _REGISTRIES: Dict[str, Dict[str, type]] = {r: {} for r in ROLES}
 
 
@@ -47,4 +47,6 @@ def build(role: str, spec) -> "object":
         nested[slot] = build(sub_role, sub)
     part = cls(**spec.params, **nested)
     part.prefix = spec.prefix
+    if getattr(spec, "names", None):
+        part.names = dict(spec.names)
     return part

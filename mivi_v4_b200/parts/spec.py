@@ -35,6 +35,10 @@ class PartSpec:
     params: dict = field(default_factory=dict)  # constructor arguments (sizes, constants)
     prefix: str = ""                            # tensor-name prefix in the checkpoint
     parts: Dict[str, "PartSpec"] = field(default_factory=dict)   # nested parts (a mixer's position encoding)
+    # local tensor name -> full checkpoint name, for tensors whose name is not ``prefix`` + local name
+    # (a checkpoint that calls its embedding table just "embed").  A tensor named here may be shared:
+    # several parts may give the same checkpoint name with the same shape, and each is handed the tensor.
+    names: Dict[str, str] = field(default_factory=dict)
 
 
 @dataclass

@@ -33,7 +33,7 @@ def main(argv: Optional[Sequence[str]] = None, stdin=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens that live requests hold at any time, each request rounded up to 64")
+                    help="most tokens that live requests hold at any time")
     args = ap.parse_args(argv)
 
     import torch
@@ -44,7 +44,10 @@ def main(argv: Optional[Sequence[str]] = None, stdin=None) -> int:
         return 2
     os.makedirs(args.out, exist_ok=True)
     model = load_model(args.model, args.dtype, "cuda:0")
-    engine = Engine(model, max_tokens=max(64, args.max_tokens), page_size=64)
+    # every live request may hold one page that is only partly filled, beyond the tokens it was counted for
+    page_size, most_requests = 64, 256
+    engine = Engine(model, max_tokens=max(page_size, args.max_tokens) + page_size * most_requests, max_batch=most_requests,
+                    page_size=page_size)
     slots = {}
     for line in (sys.stdin if stdin is None else stdin):
         line = line.strip()

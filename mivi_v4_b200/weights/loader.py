@@ -59,7 +59,8 @@ def check_entries(where: str, expected: Dict[str, ParamSpec], entries: Dict[str,
         e = entries.get(n)
         if e is None:
             continue
-        if tuple(e.shape) != tuple(spec.shape):
+        # a None in a declared shape stands for a size that the checkpoint itself gives
+        if len(e.shape) != len(spec.shape) or any(w is not None and w != g for g, w in zip(e.shape, spec.shape)):
             wrong_shape.append((n, tuple(e.shape), tuple(spec.shape)))
         ok = _INT if spec.role == "table" else _FLOAT
         if e.dtype not in ok:

@@ -50,6 +50,9 @@ def random_tensors(expected: Dict[str, ParamSpec], seed: int, store_dtype: torch
     out: Dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
         store = (store_overrides or {}).get(name, store_dtype)
+        if any(d is None for d in spec.shape):
+            raise ValueError(f"the size of {name} {list(spec.shape)} is left to the checkpoint; random weights need "
+                             f"it in the configuration")
         if spec.role == "table":
             out[name] = torch.zeros(spec.shape, dtype=torch.int32)
         elif spec.init == "zeros":
