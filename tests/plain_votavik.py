@@ -3,6 +3,10 @@ cache, no batching, one function per mechanism, in float64 unless asked
 otherwise.  It shares no code with the package; the tests compare the package
 against it.
 
+``rnd`` (default: nothing) is applied where a run in a narrower dtype stores an activation between two
+kernels (a product's operand, the cached keys and values); with ``round_to(torch.bfloat16)`` the
+difference to the unrounded result estimates the rounding noise of such a run.
+
 Notation: x is the residual stream [T, W] of one sequence, h a sublayer's
 normed input, ``w`` a dict of tensors by checkpoint name, ``c`` a layer's
 entry of config.json's ``layers``.
@@ -15,6 +19,14 @@ from typing import Dict, List, Optional
 import torch
 
 F64 = torch.float64
+
+
+def same(x):
+    return x
+
+
+def round_to(dtype):
+    return lambda x: x.to(dtype).to(x.dtype)
 
 
 def layer_norm(x, weight, eps):
@@ -49,7 +61,7 @@ def decayed_outer_scan(q, k, v, decay):
     return torch.stack(out) if out else torch.zeros(0, v.shape[1], dtype=q.dtype), S
 
 
-def gla_mixer(h, w, pre, c, eps):
+def gla_mixer(h, w, pre, c, eps, rnd=same):
     """Gated linear attention with a learned decay per key channel."""
     m = c["mixer"]
     H, dk, dv, tau = m["heads"], m["dim"], m["vdim"], float(m["tau"])
@@ -57,7 +69,7 @@ def gla_mixer(h, w, pre, c, eps):
     q = (h @ w[pre + "q"].T) * dk ** -0.5
     k = h @ w[pre + "k"].T
     v = h @ w[pre + "v"].T
-    z = (h @ w[pre + "a1"].T) @ w[pre + "a2"].T + w[pre + "a2.b"]
+    z = rnd(h @ w[pre + "a1"].T) @ w[pre + "a2"].T + w[pre + "a2.b"]
     alpha = torch.sigmoid(z) ** (1.0 / tau)
     q, k, alpha, v = q.view(T, H, dk), k.view(T, H, dk), alpha.view(T, H, dk), v.view(T, H, dv)
     heads = []
@@ -65,10 +77,10 @@ def gla_mixer(h, w, pre, c, eps):
         o, _ = decayed_outer_scan(q[:, a], k[:, a], v[:, a], alpha[:, a])
         heads.append(rms_unit(o, eps) * w[pre + "norm"])
     o = torch.cat(heads, dim=-1)
-    return (o * silu(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    return rnd(o * silu(h @ w[pre + "g"].T)) @ w[pre + "o"].T
 
 
-def lightning_mixer(h, w, pre, c, eps):
+def lightning_mixer(h, w, pre, c, eps, rnd=same):
     """Linear attention with one fixed decay per head."""
     m = c["mixer"]
     H, dk, dv = m["heads"], m["dim"], m["vdim"]
@@ -82,7 +94,7 @@ def lightning_mixer(h, w, pre, c, eps):
         o, _ = decayed_outer_scan(q[:, a], k[:, a], v[:, a], decay)
         heads.append(o)
     o = rms_unit(torch.cat(heads, dim=-1), eps) * w[pre + "norm"]
-    return (o * torch.sigmoid(h @ w[pre + "g"].T)) @ w[pre + "o"].T
+    return rnd(o * torch.sigmoid(h @ w[pre + "g"].T)) @ w[pre + "o"].T
 
 
 def rotate_partial(x, positions, dims, base):
@@ -102,7 +114,7 @@ def visible(i: int, j: int, size: int, keep_first: int) -> bool:
     return j <= i and (i - j < size or j < keep_first)
 
 
-def attention_mixer(h, w, pre, c, eps, positions=None):
+def attention_mixer(h, w, pre, c, eps, rnd=same, positions=None):
     """Softmax attention: grouped heads, norm over the whole q and k projections, partial rotation,
     capped scores, a window that keeps the first tokens, a sink in the denominator, a gate per head."""
     m = c["mixer"]
@@ -111,10 +123,10 @@ def attention_mixer(h, w, pre, c, eps, positions=None):
     pos = torch.arange(T) if positions is None else positions
     q = rms_unit(h @ w[pre + "q"].T, eps) * w[pre + "q.norm"]
     k = rms_unit(h @ w[pre + "k"].T, eps) * w[pre + "k.norm"]
-    v = (h @ w[pre + "v"].T).view(T, G, dv)
+    v = rnd(h @ w[pre + "v"].T).view(T, G, dv)
     rot = m.get("rot") or {"dims": 0, "base": 1.0}
-    q = rotate_partial(q.view(T, H, dk), pos, int(rot["dims"]), rot["base"])
-    k = rotate_partial(k.view(T, G, dk), pos, int(rot["dims"]), rot["base"])
+    q = rnd(rotate_partial(q.view(T, H, dk), pos, int(rot["dims"]), rot["base"]))
+    k = rnd(rotate_partial(k.view(T, G, dk), pos, int(rot["dims"]), rot["base"]))
     cap = float(m.get("softcap") or 0.0)
     size, keep = int(m["mask"]["size"]), int(m["mask"]["keep_first"])
     mask = torch.tensor([[visible(int(pos[i]), int(pos[j]), size, keep) for j in range(T)] for i in range(T)])
@@ -131,22 +143,22 @@ def attention_mixer(h, w, pre, c, eps, positions=None):
         e = torch.exp(s - top)
         p = e / (e.sum(-1, keepdim=True) + torch.exp(sink - top))
         heads.append((p @ v[:, kv]) * gate[:, a:a + 1])
-    return torch.cat(heads, dim=-1) @ w[pre + "o"].T
+    return rnd(torch.cat(heads, dim=-1)) @ w[pre + "o"].T
 
 
-def dense_ff(h, w, pre, c):
+def dense_ff(h, w, pre, c, rnd=same):
     limit = float(c["mlp"]["limit"])
     g = torch.clamp(h @ w[pre + "gate"].T, max=limit)
     u = torch.clamp(h @ w[pre + "up"].T, -limit, limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[pre + "down"].T
+    return rnd(g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w[pre + "down"].T
 
 
-def token_side(x, tokens, w, layer: int, dim: int, eps):
+def token_side(x, tokens, w, layer: int, dim: int, eps, rnd=same):
     """The per-layer token input: returns what is added to x."""
     pre = f"l{layer}.side."
     e = w["side.embed"][tokens][:, layer * dim:(layer + 1) * dim]
-    g = gelu_tanh(x @ w[pre + "gate"].T) * e
-    y = g @ w[pre + "proj"].T
+    g = gelu_tanh(rnd(x) @ w[pre + "gate"].T) * e
+    y = rnd(g) @ w[pre + "proj"].T
     return rms_unit(y, eps) * w[pre + "norm"]
 
 
@@ -154,7 +166,7 @@ MIXERS = {"gla": gla_mixer, "lightning": lightning_mixer, "attention": attention
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=F64,
-            return_layers: bool = False):
+            return_layers: bool = False, rnd=same):
     """Logits [T, vocab] of one whole sequence (and the residual stream after every layer)."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in weights.items()}
     eps = float(cfg["norm"]["eps"])
@@ -164,14 +176,14 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
     layers = []
     for i, c in enumerate(cfg["layers"]):
         pre = f"l{i}."
-        h = layer_norm(x, w[pre + "norm1"], eps)
-        x = x + MIXERS[c["type"]](h, w, pre + "mix.", c, eps)
+        h = rnd(layer_norm(x, w[pre + "norm1"], eps))
+        x = x + MIXERS[c["type"]](h, w, pre + "mix.", c, eps, rnd)
         if c.get("mlp") is not None:
-            x = x + dense_ff(layer_norm(x, w[pre + "norm2"], eps), w, pre + "mlp.", c)
+            x = x + dense_ff(rnd(layer_norm(x, w[pre + "norm2"], eps)), w, pre + "mlp.", c, rnd)
         if side_dim:
-            x = x + token_side(x, toks, w, i, side_dim, eps)
+            x = x + token_side(x, toks, w, i, side_dim, eps, rnd)
         layers.append(x)
-    logits = layer_norm(x, w["final.norm"], eps) @ w["head"].T
+    logits = rnd(layer_norm(x, w["final.norm"], eps)) @ w["head"].T
     return (logits, torch.stack(layers)) if return_layers else logits
 
 
