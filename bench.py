@@ -7,6 +7,7 @@ prefill, then generation timed without its first token).
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers 16]
     python bench.py --workload unequal32 | long32k      (the two further workloads, the same line for each)
     python bench.py --stages decode|prefill [--batch B] (where a step's time goes, by stage and kernel)
+    python bench.py --design votavik [--stages ..]      (the Votavik decoder beside the LFM2 model of equal sizes)
     python bench.py --kernel NAME [--m .. --n .. --k ..] (one kernel alone, for timing and for profilers)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
@@ -188,6 +189,79 @@ WORKLOADS = {
 }
 
 
+# The Votavik decoder at sizes that resemble a real model's layers, each beside the LFM2 model of the same
+# width, depth, vocabulary, feed-forward width and attention heads: name -> (width, layers, heads, kv heads,
+# feed-forward width, vocabulary).  A third of the layers of each kind; the attention layers carry the feed-forward.
+DESIGN_SIZES = {
+    "w1024": (1024, 12, 16, 8, 4096, 32768),
+    "w2048": (2048, 15, 32, 8, 8192, 65536),
+}
+
+
+def votavik_config(width, layers, heads, kv_heads, ff, vocab):
+    gla = {"type": "gla", "mlp": None,
+           "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+    att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff, "limit": 7.0},
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 96, "vdim": 64, "scale": 96 ** -0.5, "softcap": 50.0,
+                     "mask": {"size": 1024, "keep_first": 64}, "rot": {"dims": 64, "base": 10000.0}}}
+    n_light = max(1, width // 128)
+    lig = {"type": "lightning", "mlp": None,
+           "mixer": {"heads": n_light, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * i / n_light) for i in range(n_light)]}}
+    return {"architecture": "Votavik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": 64},
+            "layers": [(gla, att, lig)[i % 3] for i in range(layers)]}
+
+
+def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
+    cfg = dict(BENCH_CONFIG)
+    cfg.update(hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
+               vocab_size=vocab, block_ff_dim=ff, block_auto_adjust_ff_dim=False,
+               layer_types=["full_attention" if i % 3 == 1 else "conv" for i in range(layers)])
+    return cfg
+
+
+def run_design(args, warmup: int) -> int:
+    """Prefill and decode throughput of the Votavik decoder at the sizes of DESIGN_SIZES, each beside the LFM2
+    model of equal sizes, random weights, bfloat16: one JSON line.  With --stages: where a step of the
+    w2048 Votavik model goes, kernel by kernel."""
+    import torch
+    from mivi_v4_b200 import measure, random_model
+    pk, pk_src = peaks()
+    if args.stages:
+        model = random_model(votavik_config(*DESIGN_SIZES["w2048"]), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+        lens = [args.tokens] if args.stages == "prefill" else [args.prompt_len] * args.batch
+        rep = measure.stage_report(model, lens, prefill=args.stages == "prefill")
+        measure.print_stage_report(rep, f"{args.stages} step, {len(lens)} sequence(s) of {lens[0]} tokens, Votavik w2048", pk)
+        return 0
+    steps = 32 if args.steps is None else args.steps
+    rows = {}
+    with ClockSampler() as clk:
+        for name, sizes in DESIGN_SIZES.items():
+            for which, cfg in (("votavik", votavik_config(*sizes)), ("lfm2", lfm2_like(*sizes))):
+                model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+                nums = measure.model_numbers(model)
+                row = {"weight_gb": nums["weight_bytes"] / 1e9}
+                for b in (8, 64):
+                    r = measure.decode_run(model, [PROMPT] * b, steps, warmup, room_each=CONTEXT)
+                    pt = decode_point(nums, r, b, pk)
+                    row[f"decode_b{b}_tok_s"], row[f"decode_b{b}_ms"], row[f"decode_b{b}_frac_hbm"] = \
+                        pt["value"], pt["ms_per_step"], pt["frac"]
+                for T in (512, PREFILL_TOKENS):
+                    ms = measure.prefill_run(model, T, reps=5, warmup=3)
+                    flops = T * nums["gemm_flops_per_token"] + nums["head_flops_per_row"] + nums["attn_flops"](T)
+                    row[f"prefill_{T}_tok_s"], row[f"prefill_{T}_ms"] = T / (ms * 1e-3), ms
+                    row[f"prefill_{T}_frac_bf16"] = flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+                rows[f"{name}/{which}"] = row
+                del model
+                torch.cuda.empty_cache()
+    print(json.dumps({"metric": "prefill and decode tokens/s of the Votavik decoder beside LFM2 at equal sizes, bf16, "
+                                "random weights", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+                      "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)", "peaks": pk_src,
+                      "sizes": {k: dict(zip(("width", "layers", "heads", "kv_heads", "ff", "vocab"), v))
+                                for k, v in DESIGN_SIZES.items()},
+                      "clocks": clk.summary(), "rows": rows}))
+    return 0
+
+
 def workload_lengths(which: str):
     import torch
     if which == "long32k":
@@ -271,6 +345,8 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the further points and the end-to-end run")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
+    ap.add_argument("--design", default=None, choices=["votavik"],
+                    help="measure the Votavik decoder beside the LFM2 model of equal sizes instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],
                     help="print where the time of a decode step (of --batch sequences) or of the prefill goes")
     ap.add_argument("--prompt-len", type=int, default=PROMPT,
@@ -315,6 +391,8 @@ def main() -> int:
         return 0
     if args.workload:
         return run_workload(args.workload, args.steps, warmup)
+    if args.design:
+        return run_design(args, warmup)
 
     steps = 64 if args.steps is None else args.steps
     cfg = dict(BENCH_CONFIG)

@@ -101,13 +101,15 @@ MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const
 }
 
 // ------------------------------------------------------------------ attention
-// One warp per (token, query head).  The keys a query reads are the kept first ones [0, keep) and
-// the window [lo, pos], walked as one run of 32 at a time: each lane scores one key, the warp agrees
-// on the running maximum, then the lanes split the value's elements for the weighted sum.  The sink
-// starts the running maximum and the denominator (its own term is exp(sink - max)), so it is counted
-// once and needs no key.
+// One block of four warps per (token, query head).  The keys a query reads are the kept first ones
+// [0, keep) and the window [lo, pos], walked as one run, 32 at a time; the runs are dealt out to the four
+// warps in turn.  In a run each lane scores one key, the warp agrees on the running maximum, then the
+// lanes split the value's elements for the weighted sum.  The sink starts the first warp's running maximum
+// and denominator (its own term is exp(sink - max)), so it is counted once and needs no key.  The four
+// partial results are merged in a fixed order, so a position's result depends on nothing but its keys.
+#define AS_WARPS 4
 template <typename T, bool VEC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(AS_WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
                       const int* __restrict__ page_table, int table_stride, int page_shift,
                       const int* __restrict__ positions, const int* __restrict__ seq_of,
@@ -115,11 +117,11 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
                       T* __restrict__ o, int N, int nh, int nkv, int dk, int dv, float scale, float cap, int window,
                       int keep_first) {
     mv_pdl_begin();
-    __shared__ float qs[4][AS_MAX_DIM];
+    __shared__ float qs[AS_MAX_DIM];
+    __shared__ float part_acc[AS_WARPS][AS_MAX_DIM];
+    __shared__ float part_m[AS_WARPS], part_l[AS_WARPS];
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long warp = (long long)blockIdx.x * 4 + wib;
-    if (warp >= (long long)N * nh) return;
-    const int n = (int)(warp / nh), h = (int)(warp - (long long)n * nh);
+    const int n = blockIdx.x / nh, h = blockIdx.x - n * nh;
     const int g = h / (nh / nkv);
     const int pos = positions[n];
     const int page_size = 1 << page_shift;
@@ -127,20 +129,20 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
     const size_t v_base = (size_t)nkv * page_size * dk;
 
     const T* qrow = q + ((size_t)n * nh + h) * dk;
-    for (int d = lane; d < dk; d += 32) qs[wib][d] = mv_to_f32(qrow[d]);
-    __syncwarp();
+    for (int d = threadIdx.x; d < dk; d += AS_WARPS * 32) qs[d] = mv_to_f32(qrow[d]);
+    __syncthreads();
 
     float acc[AS_MAX_DIM / 32];
 #pragma unroll
     for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] = 0.f;
-    float m = sinks ? sinks[h] : -INFINITY;
-    float l = sinks ? 1.f : 0.f;
+    float m = (sinks && wib == 0) ? sinks[h] : -INFINITY;
+    float l = (sinks && wib == 0) ? 1.f : 0.f;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int keep = min(keep_first, lo);
     const int total = keep + (pos - lo + 1);
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
-    for (int u0 = 0; u0 < total; u0 += 32) {
+    for (int u0 = wib * 32; u0 < total; u0 += AS_WARPS * 32) {
         const int u = u0 + lane;
         const bool valid = u < total;
         const int t = u < keep ? u : lo + (u - keep);
@@ -158,17 +160,17 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
                     float kv[8];
                     mv_load8(krow + d, kv);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[wib][d + e], kv[e], dot);
+                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
                 }
             } else {
-                for (int d = 0; d < dk; ++d) dot = fmaf(qs[wib][d], mv_to_f32(krow[d]), dot);
+                for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], mv_to_f32(krow[d]), dot);
             }
             s = dot * scale;
             if (cap > 0.f) s = cap * tanhf(s * inv_cap);
         }
         const float m_new = fmaxf(m, mv_warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
-        const float corr = expf(m - m_new);          // 0 on the first run when there is no sink (m = -inf)
+        const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
         l = l * corr + mv_warp_sum(p);
 #pragma unroll
         for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] *= corr;
@@ -184,13 +186,32 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             }
         }
     }
-    float mul = 1.0f / l;
-    if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h]));
-    T* orow = o + ((size_t)n * nh + h) * dv;
+    // merge the four warps' partial results: warp 0 always has a finite maximum or a key (the query's own
+    // key lies in some warp's run; with no sink a warp that saw no key holds m = -inf and weighs nothing)
+    if (lane == 0) { part_m[wib] = m; part_l[wib] = l; }
 #pragma unroll
     for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
         const int d = lane + 32 * r;
-        if (d < dv) orow[d] = mv_from_f32<T>(acc[r] * mul);
+        if (d < dv) part_acc[wib][d] = acc[r];
+    }
+    __syncthreads();
+    float M = part_m[0];
+#pragma unroll
+    for (int w = 1; w < AS_WARPS; ++w) M = fmaxf(M, part_m[w]);
+    float L = 0.f, wgt[AS_WARPS];
+#pragma unroll
+    for (int w = 0; w < AS_WARPS; ++w) {
+        wgt[w] = part_m[w] == -INFINITY ? 0.f : expf(part_m[w] - M);
+        L = fmaf(part_l[w], wgt[w], L);
+    }
+    float mul = 1.0f / L;
+    if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h]));
+    T* orow = o + ((size_t)n * nh + h) * dv;
+    for (int d = threadIdx.x; d < dv; d += AS_WARPS * 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < AS_WARPS; ++w) v = fmaf(part_acc[w][d], wgt[w], v);
+        orow[d] = mv_from_f32<T>(v * mul);
     }
 }
 
@@ -205,11 +226,11 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    const unsigned blocks = (unsigned)(((long long)N * nh + 3) / 4);
+    const unsigned blocks = (unsigned)((long long)N * nh);
     const int esize = dtype == MV_DT_BF16 ? 2 : 4;
     const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;
 #define AS_LAUNCH(T, V)                                                                                              \
-    mv_launch(attention_sink_kernel<T, V>, blocks, 128, 0, stream, (const T*)q, (const T*)pool, page_stride,          \
+    mv_launch(attention_sink_kernel<T, V>, blocks, AS_WARPS * 32, 0, stream, (const T*)q, (const T*)pool, page_stride,          \
               page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N, nh, nkv, dk,  \
               dv, scale, cap, window, keep_first)
     if (dtype == MV_DT_BF16) {

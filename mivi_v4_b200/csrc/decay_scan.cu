@@ -125,3 +125,224 @@ MV_API int mv_decay_scan(const float* q, int ldq, const float* k, int ldk, const
                   head_decay, inv_tau, q_scale, act, state, slots, cu, o, n_heads, dk, dv);
     return mv_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same recurrence for steps that bring many tokens a sequence, in chunks of DC_CHUNK tokens:
+// what a token reads from the tokens of its own chunk and what it reads from the state before the
+// chunk are separated, so that only the state's hand-over from chunk to chunk is sequential.  With
+// c_t the sum of log a over the chunk's tokens up to t (per key channel; all of it <= 0),
+//
+//     o_t  = sum_i q_t,i e^(c_t,i) S0[i, :]  +  sum_{s <= t} P[t, s] v_s ,
+//     P[t, s] = sum_i q_t,i k_s,i e^(c_t,i - c_s,i) ,
+//     S_end[i, :] = e^(c_last,i) S0[i, :] + sum_s k_s,i e^(c_last,i - c_s,i) v_s .
+//
+// Every exponent is a difference of cumulative logarithms taken the right way round, so every factor
+// lies in (0, 1]: nothing overflows however small a decay is.  All of it is float32 on the CUDA cores.
+// The first kernel prepares, per (sequence, head, chunk), the decayed q and k, the chunk's total decay
+// and P; the second walks a sequence's chunks with the state in registers.
+//
+// Chunks are numbered floor(cu[b] / DC_CHUNK) + b + c for chunk c of the step's sequence b: distinct
+// numbers below N / DC_CHUNK + n_seqs + 1 that need nothing from the host.
+#define DC_CHUNK 32
+#define DC_COLS 32
+#define DC_THREADS 256
+
+__global__ void __launch_bounds__(DC_THREADS)
+decay_chunk_prepare_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                           const float* __restrict__ z, int ldz, const float* __restrict__ head_decay, float inv_tau,
+                           float q_scale, int act, const int* __restrict__ cu, float* __restrict__ qd,
+                           float* __restrict__ kd, float* __restrict__ ed, float* __restrict__ P, int n_heads, int dk) {
+    mv_pdl_begin();
+    extern __shared__ float smem[];
+    const int lds = dk + 1;                         // odd row stride: rows of different tokens fall into different banks
+    float* cs = smem;                               // [DC_CHUNK][lds] cumulative log decay
+    float* qa = cs + DC_CHUNK * lds;                // activated, scaled q
+    float* ka = qa + DC_CHUNK * lds;                // activated k
+    const int c = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int row0 = cu[b], len = cu[b + 1] - row0;
+    if (c * DC_CHUNK >= len) return;
+    const int nt = min(DC_CHUNK, len - c * DC_CHUNK);
+    const int first = row0 + c * DC_CHUNK;
+    const int chunk = row0 / DC_CHUNK + b + c;
+    const int tid = threadIdx.x;
+    const float log_hd = head_decay ? logf(head_decay[h]) : 0.f;
+    for (int idx = tid; idx < nt * dk; idx += DC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        const size_t row = (size_t)(first + t);
+        float qv = q[row * ldq + (size_t)h * dk + i], kv = k[row * ldk + (size_t)h * dk + i];
+        if (act) { qv = ds_silu(qv); kv = ds_silu(kv); }
+        qa[t * lds + i] = qv * q_scale;
+        ka[t * lds + i] = kv;
+        cs[t * lds + i] = z ? ds_log_sigmoid(z[row * ldz + (size_t)h * dk + i]) * inv_tau : log_hd;
+    }
+    __syncthreads();
+    for (int i = tid; i < dk; i += DC_THREADS) {
+        float run = 0.f;
+        for (int t = 0; t < nt; ++t) {
+            run += cs[t * lds + i];
+            cs[t * lds + i] = run;
+        }
+    }
+    __syncthreads();
+    const int width = n_heads * dk;
+    for (int idx = tid; idx < nt * dk; idx += DC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        const size_t at = (size_t)(first + t) * width + (size_t)h * dk + i;
+        qd[at] = qa[t * lds + i] * expf(cs[t * lds + i]);
+        kd[at] = ka[t * lds + i] * expf(cs[(nt - 1) * lds + i] - cs[t * lds + i]);
+    }
+    for (int i = tid; i < dk; i += DC_THREADS) ed[(size_t)chunk * width + (size_t)h * dk + i] = expf(cs[(nt - 1) * lds + i]);
+    float* Pc = P + ((size_t)chunk * n_heads + h) * DC_CHUNK * DC_CHUNK;
+    for (int p = tid; p < DC_CHUNK * DC_CHUNK; p += DC_THREADS) {
+        const int t = p / DC_CHUNK, s = p - t * DC_CHUNK;
+        float sum = 0.f;
+        if (s <= t && t < nt) {
+            const float* ct = cs + t * lds;
+            const float* cq = cs + s * lds;
+            const float* qt = qa + t * lds;
+            const float* kt = ka + s * lds;
+            for (int i = 0; i < dk; ++i) sum = fmaf(qt[i] * kt[i], expf(ct[i] - cq[i]), sum);
+        }
+        Pc[p] = sum;
+    }
+}
+
+template <int R>     // key channels a warp holds of every column: dk <= 8 * R
+__global__ void __launch_bounds__(DC_THREADS)
+decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ kd, const float* __restrict__ ed,
+                        const float* __restrict__ P, const float* __restrict__ v, int ldv, int act,
+                        float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
+                        float* __restrict__ o, int n_heads, int dk, int dv) {
+    mv_pdl_begin();
+    constexpr int DKP = 8 * R;
+    extern __shared__ __align__(16) float smem[];
+    float* qt = smem;                               // [DC_CHUNK][DKP], zero beyond dk
+    float* kt = qt + DC_CHUNK * DKP;
+    float* vt = kt + DC_CHUNK * DKP;                // [DC_CHUNK][DC_COLS]
+    float* pt = vt + DC_CHUNK * DC_COLS;            // [DC_CHUNK][DC_CHUNK]
+    float* et = pt + DC_CHUNK * DC_CHUNK;           // [DKP]
+    float* red = et + DKP;                          // [8][DC_CHUNK][DC_COLS]
+    const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const int j = tile * DC_COLS + lane;
+    const int row0 = cu[b], len = cu[b + 1] - row0;
+    if (len <= 0) return;
+    const int slot = mv_read_slot(slots[b]);
+    const int width = n_heads * dk;
+    float* srow = state + (((size_t)slot * n_heads + h) * dv + (j < dv ? j : 0)) * dk;
+    float S[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const int i = w * R + r;
+        S[r] = (j < dv && i < dk) ? srow[i] : 0.f;
+    }
+    const int n_chunks = (len + DC_CHUNK - 1) / DC_CHUNK;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int nt = min(DC_CHUNK, len - c * DC_CHUNK);
+        const int first = row0 + c * DC_CHUNK;
+        const int chunk = row0 / DC_CHUNK + b + c;
+        __syncthreads();
+        for (int idx = tid; idx < DC_CHUNK * DKP; idx += DC_THREADS) {
+            const int t = idx / DKP, i = idx - t * DKP;
+            const bool in = t < nt && i < dk;
+            const size_t at = (size_t)(first + t) * width + (size_t)h * dk + i;
+            qt[idx] = in ? qd[at] : 0.f;
+            kt[idx] = in ? kd[at] : 0.f;
+        }
+        for (int idx = tid; idx < DC_CHUNK * DC_COLS; idx += DC_THREADS) {
+            const int t = idx / DC_COLS, col = tile * DC_COLS + (idx - t * DC_COLS);
+            float vv = (t < nt && col < dv) ? v[(size_t)(first + t) * ldv + (size_t)h * dv + col] : 0.f;
+            vt[idx] = act ? ds_silu(vv) : vv;
+        }
+        const float* Pc = P + ((size_t)chunk * n_heads + h) * DC_CHUNK * DC_CHUNK;
+        for (int idx = tid; idx < DC_CHUNK * DC_CHUNK; idx += DC_THREADS) pt[idx] = Pc[idx];
+        for (int i = tid; i < DKP; i += DC_THREADS) et[i] = i < dk ? ed[(size_t)chunk * width + (size_t)h * dk + i] : 0.f;
+        __syncthreads();
+        // what the chunk's tokens read from the state before the chunk: this warp's key channels
+#pragma unroll 4
+        for (int t = 0; t < DC_CHUNK; ++t) {
+            const float4* q4 = reinterpret_cast<const float4*>(qt + t * DKP + w * R);
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; r += 4) {
+                const float4 x = q4[r >> 2];
+                acc = fmaf(x.x, S[r], acc); acc = fmaf(x.y, S[r + 1], acc);
+                acc = fmaf(x.z, S[r + 2], acc); acc = fmaf(x.w, S[r + 3], acc);
+            }
+            red[(w * DC_CHUNK + t) * DC_COLS + lane] = acc;
+        }
+        // the state after the chunk
+#pragma unroll
+        for (int r = 0; r < R; ++r) S[r] *= et[w * R + r];
+#pragma unroll 2
+        for (int s = 0; s < DC_CHUNK; ++s) {
+            const float vj = vt[s * DC_COLS + lane];
+            const float4* k4 = reinterpret_cast<const float4*>(kt + s * DKP + w * R);
+#pragma unroll
+            for (int r = 0; r < R; r += 4) {
+                const float4 x = k4[r >> 2];
+                S[r] = fmaf(x.x, vj, S[r]); S[r + 1] = fmaf(x.y, vj, S[r + 1]);
+                S[r + 2] = fmaf(x.z, vj, S[r + 2]); S[r + 3] = fmaf(x.w, vj, S[r + 3]);
+            }
+        }
+        __syncthreads();
+        // outputs: the eight warps' shares in a fixed order, then the chunk's own tokens
+        for (int t = w; t < nt; t += 8) {
+            float sum = 0.f;
+#pragma unroll
+            for (int ww = 0; ww < 8; ++ww) sum += red[(ww * DC_CHUNK + t) * DC_COLS + lane];
+            for (int s = 0; s <= t; ++s) sum = fmaf(pt[t * DC_CHUNK + s], vt[s * DC_COLS + lane], sum);
+            if (j < dv) o[(size_t)(first + t) * n_heads * dv + (size_t)h * dv + j] = sum;
+        }
+    }
+    if (j < dv && mv_slot_ok(slots[b])) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const int i = w * R + r;
+            if (i < dk) srow[i] = S[r];
+        }
+    }
+}
+
+template <int R>
+static int decay_chunk_scan_launch(dim3 grid, cudaStream_t stream, const float* qd, const float* kd, const float* ed,
+                                   const float* P, const float* v, int ldv, int act, float* state, const int* slots,
+                                   const int* cu, float* o, int n_heads, int dk, int dv) {
+    const size_t smem = sizeof(float) * ((size_t)2 * DC_CHUNK * 8 * R + DC_CHUNK * DC_COLS + DC_CHUNK * DC_CHUNK + 8 * R +
+                                         8 * DC_CHUNK * DC_COLS);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(decay_chunk_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    mv_launch(decay_chunk_scan_kernel<R>, grid, DC_THREADS, smem, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o,
+              n_heads, dk, dv);
+    return mv_launch_status();
+}
+
+// How many chunks the scratch of a step of N tokens in n_seqs sequences must hold.
+MV_API int mv_decay_chunks(int N, int n_seqs) { return N / DC_CHUNK + n_seqs + 1; }
+
+// Arguments as mv_decay_scan, plus the longest sequence's tokens (max_len) and scratch: qd, kd [N, n_heads * dk],
+// ed [chunks, n_heads * dk], P [chunks, n_heads, DC_CHUNK, DC_CHUNK] with chunks = mv_decay_chunks(N, n_seqs).
+MV_API int mv_decay_scan_chunked(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                 const float* z, int ldz, const float* head_decay, float inv_tau, float q_scale, int act,
+                                 float* state, const int* slots, const int* cu, float* o, float* qd, float* kd, float* ed,
+                                 float* P, int n_seqs, int max_len, int n_heads, int dk, int dv, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_len <= 0) return 0;
+    if (dk < 1 || dk > 256 || dv < 1 || (!z && !head_decay)) return (int)cudaErrorInvalidValue;
+    const size_t smem_a = sizeof(float) * (size_t)3 * DC_CHUNK * (dk + 1);
+    static size_t attr_a = 0;
+    if (smem_a > attr_a) {
+        cudaFuncSetAttribute(decay_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        attr_a = smem_a;
+    }
+    mv_launch(decay_chunk_prepare_kernel, dim3((max_len + DC_CHUNK - 1) / DC_CHUNK, n_heads, n_seqs), DC_THREADS, smem_a,
+              stream, q, ldq, k, ldk, z, ldz, head_decay, inv_tau, q_scale, act, cu, qd, kd, ed, P, n_heads, dk);
+    int code = mv_launch_status();
+    if (code) return code;
+    const dim3 grid((dv + DC_COLS - 1) / DC_COLS, n_heads, n_seqs);
+    if (dk <= 64) return decay_chunk_scan_launch<8>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    if (dk <= 128) return decay_chunk_scan_launch<16>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    return decay_chunk_scan_launch<32>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+}

@@ -27,7 +27,7 @@ def model_numbers(model) -> dict:
     head, and the attention operations of a prompt of T tokens."""
     elt = 2 if model.dtype == torch.bfloat16 else 4
     plan = model.cache_plan()
-    kv_per_token = sum(g.n_layers * 2 * g.need.n_kv_heads * g.need.head_dim * elt
+    kv_per_token = sum(g.n_layers * g.need.n_kv_heads * (g.need.head_dim + g.need.value_dim) * elt
                        for g in plan.groups if isinstance(g.need, KVNeed))
     state_per_seq = sum(g.n_layers * torch.empty(0, dtype=g.need.dtype).element_size() * math.prod(g.need.shape)
                         for g in plan.groups if not isinstance(g.need, KVNeed))
@@ -36,11 +36,22 @@ def model_numbers(model) -> dict:
         n = sum(math.prod(spec.shape) for spec in part.param_specs().values() if spec.role == "matrix")
         return n + sum(matrices(sub) for sub in part.nested().values())
     per_token = sum(matrices(model.blocks[e.block]) for e in model.schedule)
-    attn = [(b.mixer.nh, b.mixer.hd) for b in (model.blocks[e.block] for e in model.schedule)
-            if hasattr(getattr(b, "mixer", None), "nh")]
+    mixers = [getattr(model.blocks[e.block], "mixer", None) for e in model.schedule]
+
+    def mixer_flops(m, T: int) -> int:
+        """Operations of one mixer beside its projections over a prompt of T tokens."""
+        if hasattr(m, "hd") and hasattr(m, "nh"):                      # softmax attention, every earlier key
+            return 4 * m.nh * m.hd * T * (T + 1) // 2
+        if hasattr(m, "window") and hasattr(m, "dk"):                 # softmax attention, a window and kept first tokens
+            reach = m.window + m.keep_first if m.window else T
+            pairs = T * (T + 1) // 2 if reach >= T else reach * (reach + 1) // 2 + (T - reach) * reach
+            return 2 * m.nh * (m.dk + m.dv) * pairs
+        if hasattr(m, "dk") and hasattr(m, "dv"):                     # a decaying matrix state: update and read-out
+            return 5 * m.nh * m.dk * m.dv * T
+        return 0
     return dict(weight_bytes=model.weight_bytes(), kv_bytes_per_token=kv_per_token, state_bytes_per_seq=state_per_seq,
                 gemm_flops_per_token=2 * per_token, head_flops_per_row=2 * model.vocab_size * model.hidden_size,
-                attn_flops=lambda T: sum(4 * nh * hd * T * (T + 1) // 2 for nh, hd in attn))
+                attn_flops=lambda T: sum(mixer_flops(m, T) for m in mixers))
 
 
 def random_prompts(vocab: int, lengths: Sequence[int], seed: int) -> List[List[int]]:

@@ -52,6 +52,9 @@ _SIGNATURES = {
         "mv_table_gate": [_P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
         "mv_round_rows": [_P, _P, _I, _Q, _P],
         "mv_decay_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _F, _F, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_decay_chunks": [_I, _I],
+        "mv_decay_scan_chunked": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I,
+                                  _I, _I, _I, _P],
         "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_attention_sink": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I,
                               _P],
@@ -71,6 +74,8 @@ _SIGNATURES = {
         "mv_gemm_tc_swap_heads": [_P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
                                   _P, _I, _I, _I, _F, _P, _Q, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
+        "mv_attention_sink_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
+                                      _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
     },
@@ -210,7 +215,7 @@ def _fn(lib: str, name: str):
         f.argtypes = _SIGNATURES[lib][name]
         f.restype = ctypes.c_int
         _fns[key] = f
-    if _profile is not None and not name.endswith(("_partials", "_tile_rows", "_to_host", "_delay")):
+    if _profile is not None and not name.endswith(("_partials", "_tile_rows", "_to_host", "_delay", "_chunks")):
         return _profile.wrap(name, f)
     return f
 
@@ -278,7 +283,7 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
 
 _launches = 0
 # kernels launched by one call of each entry point
-_KERNELS_PER_CALL = {"mv_shortconv": 2}
+_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2}
 
 
 def launch_count() -> int:
@@ -429,6 +434,8 @@ def round_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 MAX_SCAN_KEY_DIM = 256
 SCAN_ACT_NONE, SCAN_ACT_SILU = 0, 1
+SCAN_CHUNKED_FROM = 16          # a step whose longest sequence brings this many tokens walks them in chunks
+SCAN_CHUNK = 32
 
 
 def _cols(t: torch.Tensor, name: str, n_rows: int, width: int):
@@ -443,13 +450,17 @@ def _cols(t: torch.Tensor, name: str, n_rows: int, width: int):
 def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
                cu: torch.Tensor, out: torch.Tensor, n_seqs: int, n_heads: int, dk: int, dv: int, *,
                decay_logits: Optional[torch.Tensor] = None, inv_tau: float = 1.0,
-               head_decay: Optional[torch.Tensor] = None, q_scale: float = 1.0, act: int = SCAN_ACT_NONE) -> torch.Tensor:
+               head_decay: Optional[torch.Tensor] = None, q_scale: float = 1.0, act: int = SCAN_ACT_NONE,
+               max_len: int = 1, ws=None) -> torch.Tensor:
     """Linear attention with a decaying state, per head: S <- diag(a_t) S + k_t v_t^T, o_t = S^T q_t, over the
     step's tokens in order, from and into ``state`` [slots, heads, dv, dk] (float32, transposed: a value
     column's key channels lie together).  The decay a_t is sigmoid(decay_logits)^inv_tau per token and key
     channel, or ``head_decay`` [heads], a constant per head.  q, k [N, heads * dk] and v [N, heads * dv] are
     float32 and may be column slices of one wider matrix; ``act`` is applied to all three as they are read
-    and ``q_scale`` multiplies q.  Everything is computed in float32."""
+    and ``q_scale`` multiplies q.  Everything is computed in float32.  ``max_len``: the most tokens that a
+    sequence brings; with ``ws`` (a Workspace, for scratch) steps of ``SCAN_CHUNKED_FROM`` tokens a sequence and
+    more take the kernels that walk a sequence in chunks of 32 tokens, whose sums come in another order (the
+    results differ from the token-by-token kernel's by rounding)."""
     N = out.shape[0]
     if not 1 <= dk <= MAX_SCAN_KEY_DIM:
         raise KernelError(f"decay_scan: key size {dk} is outside 1..{MAX_SCAN_KEY_DIM}")
@@ -461,6 +472,20 @@ def decay_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.T
     zp, ldz = _cols(decay_logits, "decay_scan decay logits", N, n_heads * dk) if decay_logits is not None else (None, 0)
     _need(state, "decay_scan state", torch.float32, (None, n_heads, dv, dk))
     _guard("core", "decay_scan", out.device, n_slots=state.shape[0])
+    if ws is not None and max_len >= SCAN_CHUNKED_FROM:
+        chunks = int(_fn("core", "mv_decay_chunks")(N, int(n_seqs)))
+        qd = ws.get("scan_qd", (N, n_heads * dk), torch.float32)
+        kd = ws.get("scan_kd", (N, n_heads * dk), torch.float32)
+        ed = ws.get("scan_ed", (chunks, n_heads * dk), torch.float32)
+        pm = ws.get("scan_p", (chunks, n_heads, SCAN_CHUNK, SCAN_CHUNK), torch.float32)
+        _check(_fn("core", "mv_decay_scan_chunked")(
+            qp, ldq, kp, ldk, vp, ldv, zp, ldz, _need(head_decay, "head decay", torch.float32, (n_heads,), True),
+            float(inv_tau), float(q_scale), int(act), state.data_ptr(), _need(slots, "slots", torch.int32),
+            _need(cu, "cu", torch.int32), _need(out, "decay_scan out", torch.float32, (N, n_heads * dv)),
+            qd.data_ptr(), kd.data_ptr(), ed.data_ptr(), pm.data_ptr(), int(n_seqs), int(max_len), n_heads, dk, dv,
+            _stream()), "mv_decay_scan_chunked")
+        account(N * n_heads * (6 * dk + 2 * dv) * 4 + 2 * n_seqs * n_heads * dk * dv * 4, 5 * N * n_heads * dk * dv)
+        return out
     _check(_fn("core", "mv_decay_scan")(
         qp, ldq, kp, ldk, vp, ldv, zp, ldz, _need(head_decay, "head decay", torch.float32, (n_heads,), True),
         float(inv_tau), float(q_scale), int(act), state.data_ptr(), _need(slots, "slots", torch.int32),
@@ -545,6 +570,41 @@ def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_tab
         _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
         _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), _stream()),
         "mv_attention_sink")
+    return out
+
+
+def attention_sink_prefill_supported(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """What the tensor-core kernel for steps of many query tokens takes: bfloat16, key and value sizes that are
+    multiples of 16 up to 128."""
+    return (dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= PREFILL_ATTENTION_MAX_HEAD_DIM
+            and 16 <= dv <= PREFILL_ATTENTION_MAX_HEAD_DIM)
+
+
+def attention_sink_prefill(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, cu, starts,
+                           out: torch.Tensor, n_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *,
+                           softcap: float = 0.0, window: int = 0, keep_first: int = 0,
+                           sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`attention_sink` for a step with many query tokens, on the tensor cores (bfloat16, key and value
+    sizes 16..128 in steps of 16).  The step's tokens are packed sequence by sequence (``cu``), sequence b
+    starting at position ``starts[b]``."""
+    N = q.shape[0]
+    if not attention_sink_prefill_supported(q.dtype, dk, dv):
+        raise KernelError(f"attention_sink_prefill: needs bfloat16 and key and value sizes 16..128 in steps of 16, "
+                          f"got {q.dtype}, {dk}, {dv}")
+    if nkv < 1 or nh % nkv:
+        raise KernelError(f"attention: {nh} heads are not a multiple of {nkv} kv heads")
+    _check_kv_wide(pool, nkv, page_size, dk, dv, "attention_sink_prefill")
+    if q.dtype != pool.dtype or out.dtype != q.dtype:
+        raise KernelError(f"attention: q {q.dtype}, cache {pool.dtype}, out {out.dtype} must agree")
+    gp, ldg = _cols(gate, "attention gate", N, nh) if gate is not None else (None, 0)
+    _guard("bf16", "attention_sink_prefill", q.device, n_pages=pool.shape[0])
+    _check(_fn("bf16", "mv_attention_sink_prefill")(
+        _need(q, "q", None, (N, nh * dk)), _need(pool, "cache pool"), pool.stride(0),
+        _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
+        _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
+        _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
+        N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), _stream()),
+        "mv_attention_sink_prefill")
     return out
 
 

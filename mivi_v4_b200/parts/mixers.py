@@ -244,7 +244,7 @@ class GatedLinearAttention(Part):
         o = self.scratch(step, "o", (N, vv), torch.float32)
         K.decay_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], view.state, step.slots, step.cu, o,
                      step.n_seqs, self.nh, self.dk, self.dv, decay_logits=z, inv_tau=1.0 / self.tau,
-                     q_scale=self.dk ** -0.5)
+                     q_scale=self.dk ** -0.5, max_len=step.max_len, ws=step.ws)
         y = self.scratch(step, "mix", (N, vv), step.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.dv, self.eps, K.GATE_SILU, y)
         linear(y, self.w_o, resid, accumulate=True)
@@ -287,7 +287,8 @@ class LightningAttention(Part):
         linear(u, self.w_qkvg, proj)
         o = self.scratch(step, "o", (N, vv), torch.float32)
         K.decay_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], view.state, step.slots, step.cu, o,
-                     step.n_seqs, self.nh, self.dk, self.dv, head_decay=self.decay_t, act=K.SCAN_ACT_SILU)
+                     step.n_seqs, self.nh, self.dk, self.dv, head_decay=self.decay_t, act=K.SCAN_ACT_SILU,
+                     max_len=step.max_len, ws=step.ws)
         y = self.scratch(step, "mix", (N, vv), step.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, vv, self.eps, K.GATE_SIGMOID, y)
         linear(y, self.w_o, resid, accumulate=True)
@@ -363,13 +364,23 @@ class SinkAttention(Part):
                            view.pool, view.page_size, q, nh, nkv, dk, dv)
         o = self.scratch(step, "mix", (N, nh * dv), step.dtype)
         g0 = nh * dk + nkv * (dk + dv)
-        K.attention_sink(q, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o, nh, nkv, dk,
-                         dv, self.scale, softcap=self.softcap, window=self.window, keep_first=self.keep_first,
-                         sinks=self.sinks, gate=proj[:, g0:g0 + nh] if self.gated else None)
+        extras = dict(softcap=self.softcap, window=self.window, keep_first=self.keep_first, sinks=self.sinks,
+                      gate=proj[:, g0:g0 + nh] if self.gated else None)
+        # few query tokens, or many sequences with a token or two each: every query token on its own
+        few = N <= K.DECODE_ATTENTION_MAX_TOKENS or step.max_len <= K.DECODE_ATTENTION_MAX_QUERIES
+        if not few and K.attention_sink_prefill_supported(step.dtype, dk, dv):
+            K.attention_sink_prefill(q, view.pool, view.page_size, view.page_table, step.cu, step.starts, o,
+                                     step.n_seqs, nh, nkv, dk, dv, self.scale, **extras)
+        else:
+            K.attention_sink(q, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o, nh, nkv,
+                             dk, dv, self.scale, **extras)
         if K.profiling_on():
             reach = (self.window + self.keep_first) if self.window else None
             pairs = sum(sum(min(s + i + 1, reach) if reach else s + i + 1 for i in range(n))
                         for s, n in zip(step.host_starts, step.host_lens))
-            K.account(nkv * (dk + dv) * view.pool.element_size() * pairs + N * nh * (dk + dv) * q.element_size(),
+            # keys and values: every query reads its own in a step of few tokens, a sequence's tile shares them otherwise
+            rows = pairs if few else sum(min(s + n, n + reach) if reach else s + n
+                                         for s, n in zip(step.host_starts, step.host_lens))
+            K.account(nkv * (dk + dv) * view.pool.element_size() * rows + N * nh * (dk + dv) * q.element_size(),
                       2 * nh * (dk + dv) * pairs)
         linear(o, self.w_o, resid, accumulate=True)

@@ -127,6 +127,62 @@ def test_decay_scan_with_a_decay_per_channel(heads, dk, dv):
     assert torch.isnan(state[1]).all() and torch.isnan(state[2]).all()          # other slots untouched
 
 
+class _Scratch:
+    """What the chunked kernels ask of a workspace."""
+    def __init__(self):
+        self.bufs = {}
+
+    def get(self, name, shape, dtype):
+        self.bufs[name] = torch.full(tuple(shape), float("nan"), dtype=dtype, device=DEV)
+        return self.bufs[name]
+
+
+@pytest.mark.parametrize("heads,dk,dv,per_channel", [(2, 16, 24, True), (1, 20, 5, False), (3, 72, 40, True),
+                                                      (1, 136, 33, False), (2, 256, 64, True)])
+def test_decay_scan_in_chunks(heads, dk, dv, per_channel):
+    """Sequences of 1, 31, 32, 33 and 150 tokens in one step (chunks that are full, one short, one over), on top
+    of states that earlier steps left; decays small enough that a product over a chunk underflows."""
+    lens = [33, 1, 150, 32, 31]
+    N, B = sum(lens), len(lens)
+    q, k, v, z = _scan_case(N, heads, dk, dv, dk + 1)
+    z = z * 4 - 2                                          # sigmoid(z)^(1/tau) down to 1e-3 a token with tau 1
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    slots = torch.tensor([4, 2, 0, 5, 1], dtype=torch.int32, device=DEV)
+    hd = (torch.rand(heads) * 0.5 + 0.5).to(DEV)
+    if per_channel:
+        decay = torch.sigmoid(z.double().cpu())
+        kw = dict(decay_logits=z, inv_tau=1.0, q_scale=0.7)
+        qs = q * 0.7
+    else:
+        decay = hd.double().cpu().repeat_interleave(dk)[None, :].expand(N, -1)
+        kw = dict(head_decay=hd, act=K.SCAN_ACT_SILU)
+        qs = q
+    # the state every sequence starts from: what a first step of 5 tokens left (token by token kernel)
+    q0, k0, v0, z0 = _scan_case(5 * B, heads, dk, dv, 99)
+    state = torch.zeros((6, heads, dv, dk), device=DEV)
+    o0 = torch.empty((5 * B, heads * dv), device=DEV)
+    cu0 = torch.arange(0, 5 * B + 1, 5, dtype=torch.int32, device=DEV)
+    kw0 = dict(kw, decay_logits=z0) if per_channel else kw
+    K.decay_scan(q0, k0, v0, state, slots, cu0, o0, B, heads, dk, dv, **kw0)
+    seq = state.clone()
+    out_seq = torch.empty((N, heads * dv), device=DEV)
+    K.decay_scan(q, k, v, seq, slots, cu, out_seq, B, heads, dk, dv, **kw)                 # token by token
+    out = torch.full((N, heads * dv), float("nan"), device=DEV)
+    K.decay_scan(q, k, v, state, slots, cu, out, B, heads, dk, dv, max_len=max(lens), ws=_Scratch(), **kw)
+    scale = out_seq.abs().max().item()
+    assert torch.isfinite(out).all()
+    assert (out - out_seq).abs().max().item() <= 2e-5 * scale
+    assert (state - seq).abs().max().item() <= 2e-5 * seq.abs().max().item()
+    assert torch.equal(state[3], torch.zeros_like(state[3]))                               # a slot of no sequence
+    # and against the plain scan from a zero state (the first sequence's first step left out: fresh slots)
+    fresh = torch.zeros((6, heads, dv, dk), device=DEV)
+    K.decay_scan(q, k, v, fresh, slots, cu, out, B, heads, dk, dv, max_len=max(lens), ws=_Scratch(), **kw)
+    want_o, want_s = _plain_scan(qs, k, v, decay, lens, heads, dk, dv, act=not per_channel)
+    close(out, want_o, torch.float32, "outputs")
+    for b, s in enumerate(slots.tolist()):
+        close(fresh[s], want_s[b], torch.float32, f"state of sequence {b}")
+
+
 def test_decay_scan_any_cut_gives_the_same_numbers_and_slots_are_reused():
     heads, dk, dv = 2, 24, 20
     lens = [37]
@@ -228,6 +284,62 @@ def test_attention_sink_window_edges_far_keys_and_the_sink(nh, nkv, dk, dv, wind
     K.attention_sink(q.reshape(N, -1).to(dtype).to(DEV), pool, ps, table, pos_t, seq_of, out, nh, nkv, dk, dv, scale,
                      softcap=cap, window=window, keep_first=keep)
     close(out, _plain_attention(qq, kq, vq, nh, nkv, scale, cap, window, keep, None, None, positions), dtype, "plain")
+
+
+@pytest.mark.parametrize("nh,nkv,dk,dv,window,keep,cap", [
+    (4, 2, 16, 32, 9, 3, 20.0), (3, 1, 96, 32, 0, 0, 0.0), (2, 2, 48, 80, 64, 64, 5.0), (2, 1, 128, 128, 130, 70, 0.0),
+    (2, 1, 64, 112, 70, 129, 30.0)])
+def test_attention_sink_prefill_on_tensor_cores(nh, nkv, dk, dv, window, keep, cap):
+    """Two sequences in one step, the second one a later portion of its prompt (its first keys already cached);
+    every query against the plain expression; keys that stand out just inside and just outside the window of
+    some queries and among the kept first tokens."""
+    torch.manual_seed(dk + dv)
+    dtype, ps = torch.bfloat16, 64
+    T1, T2, start2 = 150, 333, 120
+    scale = 1.1 / math.sqrt(dk)
+    sinks, outs, wants = torch.randn(nh) * 2, [], []
+    pools, tables, qs, gates = [], [], [], []
+    for T, start in ((T1, 0), (T2, start2)):
+        k, v = torch.randn(T, nkv, dk), torch.randn(T, nkv, dv)
+        q = torch.randn(T - start, nh, dk)
+        for n in range(0, T - start, 7):                   # a loud key at the window's edges and among the kept ones
+            pos = start + n
+            for j in (pos - window + 1, pos - window, keep - 1, keep):
+                if window and 0 <= j <= pos:
+                    k[j] = k[j] * 0.3 + 2.0 * q[n, n % nh][None, :] / q[n, n % nh].norm()
+        gate = torch.randn(T - start, nh)
+        kq, vq, qq = k.to(dtype).double(), v.to(dtype).double(), q.to(dtype).double()
+        wants.append(_plain_attention(qq, kq, vq, nh, nkv, scale, cap, window, keep, sinks.double(), gate.double(),
+                                      list(range(start, T))))
+        pools.append((k, v))
+        qs.append(q.reshape(T - start, -1))
+        gates.append(gate)
+    # both sequences in one pool: the first takes pages 7, 1, 4; the second 0, 2, 8, 3, 6, 5
+    orders = ([7, 1, 4], [0, 2, 8, 3, 6, 5])
+    pool = torch.zeros((9, nkv * ps * (dk + dv)), dtype=dtype, device=DEV)
+    for (k, v), order in zip(pools, orders):
+        part, _ = _fill_cache(k, v, ps, nkv, dk, dv, dtype, order)
+        for p in order:
+            pool[p] = part[p]
+    table = torch.zeros((2, 6), dtype=torch.int32, device=DEV)
+    table[0, :3] = torch.tensor(orders[0], dtype=torch.int32)
+    table[1] = torch.tensor(orders[1], dtype=torch.int32)
+    N = T1 + T2 - start2
+    q_all = torch.cat(qs).to(dtype).to(DEV)
+    gate_all = torch.cat(gates).to(DEV)
+    cu = torch.tensor([0, T1, N], dtype=torch.int32, device=DEV)
+    starts = torch.tensor([0, start2], dtype=torch.int32, device=DEV)
+    out = torch.full((N, nh * dv), float("nan"), dtype=dtype, device=DEV)
+    K.attention_sink_prefill(q_all, pool, ps, table, cu, starts, out, 2, nh, nkv, dk, dv, scale, softcap=cap, window=window,
+                             keep_first=keep, sinks=sinks.to(DEV), gate=gate_all)
+    close(out, torch.cat(wants), dtype, "tensor-core prefill")
+    # and the kernel of single query tokens gives the same, token by token
+    positions = torch.cat([torch.arange(0, T1), torch.arange(start2, T2)]).to(torch.int32).to(DEV)
+    seq_of = torch.cat([torch.zeros(T1), torch.ones(T2 - start2)]).to(torch.int32).to(DEV)
+    out2 = torch.empty_like(out)
+    K.attention_sink(q_all, pool, ps, table, positions, seq_of, out2, nh, nkv, dk, dv, scale, softcap=cap, window=window,
+                     keep_first=keep, sinks=sinks.to(DEV), gate=gate_all)
+    close(out2, torch.cat(wants), dtype, "token by token")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
