@@ -19,10 +19,11 @@
 #define AS_MAX_DIM 256
 
 // ------------------------------------------------ prepare q, k, v of a step's tokens
-// One block per token.  proj: 32-bit rows [q (nh*dk) | k (nkv*dk) | v (nkv*dv) | ...] with row
+// A token is shared by gridDim.y blocks: each works out the two sums of squares over the whole of q and of k
+// (a few thousand values) and then finishes its share of the elements.  proj: 32-bit rows [q (nh*dk) | k (nkv*dk) | v (nkv*dv) | ...] with row
 // stride ld.  q goes to q_out in the model's dtype, k and v into the token's row of its page.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __restrict__ wq,
                         const float* __restrict__ wk, float eps, int rot_dims, const float* __restrict__ inv_freq,
                         const int* __restrict__ positions, const int* __restrict__ seq_of,
@@ -30,9 +31,13 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
                         long long page_stride, T* __restrict__ q_out, int nh, int nkv, int dk, int dv) {
     mv_pdl_begin();
     __shared__ float scratch[33];
+    __shared__ float rot_sn[AS_MAX_DIM / 2], rot_cs[AS_MAX_DIM / 2];
     const int n = blockIdx.x;
     const float* row = proj + (size_t)n * ld;
     const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv;
+    // the rotation of pair i at this token's position is the same for every head: worked out once
+    for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x)
+        sincosf((float)positions[n] * inv_freq[i], &rot_sn[i], &rot_cs[i]);
     const float* qr = row;
     const float* kr = row + nq;
     const float* vr = kr + nk;
@@ -49,7 +54,9 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
     T* vpage = kpage + (size_t)nkv * page_size * dk;
     const bool page_ok = mv_page_ok(page);
     const int half = rot_dims >> 1;
-    for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+    const int per = (nq + nk + nv + gridDim.y - 1) / gridDim.y;         // elements of q, k and v a block finishes
+    const int e_lo = blockIdx.y * per, e_hi = min(e_lo + per, nq + nk + nv);
+    for (int e = e_lo + threadIdx.x; e < min(e_hi, nq + nk); e += blockDim.x) {
         const bool is_q = e < nq;
         const int f = is_q ? e : e - nq;
         const float* src = is_q ? qr : kr;
@@ -62,8 +69,7 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
             const int i = d < half ? d : d - half;
             const int fp = d < half ? f + half : f - half;
             const float b = src[fp] * sc * (w ? w[fp] : 1.f);
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float sn = rot_sn[i], cs = rot_cs[i];
             a = d < half ? a * cs - b * sn : a * cs + b * sn;
         }
         if (is_q)
@@ -72,7 +78,7 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
             kpage[((size_t)head * page_size + prow) * dk + d] = mv_from_f32<T>(a);
     }
     if (page_ok)
-        for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+        for (int e = max(e_lo, nq + nk) - (nq + nk) + threadIdx.x; e < e_hi - (nq + nk); e += blockDim.x) {
             const int head = e / dv, d = e - head * dv;
             vpage[((size_t)head * page_size + prow) * dv + d] = mv_from_f32<T>(vr[e]);
         }
@@ -89,25 +95,28 @@ MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
+    // few tokens: several blocks a token, so that the step still spreads over the device
+    const int parts = N >= 256 ? 1 : (N >= 64 ? 2 : 6);
+    const dim3 grid(N, parts);
     if (dtype == MV_DT_BF16)
-        mv_launch(qkv_prepare_wide_kernel<__nv_bfloat16>, N, 128, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+        mv_launch(qkv_prepare_wide_kernel<__nv_bfloat16>, grid, 256, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
                   positions, seq_of, page_table, table_stride, page_shift, (__nv_bfloat16*)pool, page_stride,
                   (__nv_bfloat16*)q_out, nh, nkv, dk, dv);
     else
-        mv_launch(qkv_prepare_wide_kernel<float>, N, 128, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+        mv_launch(qkv_prepare_wide_kernel<float>, grid, 256, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
                   positions, seq_of, page_table, table_stride, page_shift, (float*)pool, page_stride, (float*)q_out, nh,
                   nkv, dk, dv);
     return mv_launch_status();
 }
 
 // ------------------------------------------------------------------ attention
-// One block of four warps per (token, query head).  The keys a query reads are the kept first ones
-// [0, keep) and the window [lo, pos], walked as one run, 32 at a time; the runs are dealt out to the four
+// One block of eight warps per (token, query head).  The keys a query reads are the kept first ones
+// [0, keep) and the window [lo, pos], walked as one run, 32 at a time; the runs are dealt out to the eight
 // warps in turn.  In a run each lane scores one key, the warp agrees on the running maximum, then the
 // lanes split the value's elements for the weighted sum.  The sink starts the first warp's running maximum
-// and denominator (its own term is exp(sink - max)), so it is counted once and needs no key.  The four
+// and denominator (its own term is exp(sink - max)), so it is counted once and needs no key.  The eight
 // partial results are merged in a fixed order, so a position's result depends on nothing but its keys.
-#define AS_WARPS 4
+#define AS_WARPS 8
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(AS_WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
@@ -156,6 +165,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             vaddr = (unsigned long long)(pbase + v_base + r * dv);
             float dot = 0.f;
             if (VEC) {
+#pragma unroll 4
                 for (int d = 0; d < dk; d += 8) {
                     float kv[8];
                     mv_load8(krow + d, kv);
@@ -175,18 +185,31 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
 #pragma unroll
         for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] *= corr;
         m = m_new;
+        // the values of the run's keys, eight rows requested before any is used (a row whose key is masked or
+        // beyond the run has weight 0 and is not read)
         const int cnt = min(32, total - u0);
-        for (int j = 0; j < cnt; ++j) {
-            const float pj = __shfl_sync(0xffffffffu, p, j);
-            const T* vrow = (const T*)__shfl_sync(0xffffffffu, vaddr, j);
+        for (int j0 = 0; j0 < cnt; j0 += 8) {
+            float pj[8];
+            const T* vrow[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                pj[e] = __shfl_sync(0xffffffffu, p, j0 + e);
+                vrow[e] = (const T*)__shfl_sync(0xffffffffu, vaddr, j0 + e);
+            }
 #pragma unroll
             for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
                 const int d = lane + 32 * r;
-                if (d < dv) acc[r] = fmaf(pj, mv_to_f32(vrow[d]), acc[r]);
+                if (d < dv) {
+                    float x[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) x[e] = (j0 + e < cnt) ? mv_to_f32(vrow[e][d]) : 0.f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[r] = fmaf(pj[e], x[e], acc[r]);
+                }
             }
         }
     }
-    // merge the four warps' partial results: warp 0 always has a finite maximum or a key (the query's own
+    // merge the warps' partial results: warp 0 always has a finite maximum or a key (the query's own
     // key lies in some warp's run; with no sink a warp that saw no key holds m = -inf and weighs nothing)
     if (lane == 0) { part_m[wib] = m; part_l[wib] = l; }
 #pragma unroll

@@ -144,7 +144,7 @@ MV_API int mv_decay_scan(const float* q, int ldq, const float* k, int ldk, const
 // Chunks are numbered floor(cu[b] / DC_CHUNK) + b + c for chunk c of the step's sequence b: distinct
 // numbers below N / DC_CHUNK + n_seqs + 1 that need nothing from the host.
 #define DC_CHUNK 32
-#define DC_COLS 32
+#define DC_COLS 16
 #define DC_THREADS 256
 
 __global__ void __launch_bounds__(DC_THREADS)
@@ -207,115 +207,142 @@ decay_chunk_prepare_kernel(const float* __restrict__ q, int ldq, const float* __
     }
 }
 
-template <int R>     // key channels a warp holds of every column: dk <= 8 * R
+// A block is 16 value columns of one head of one sequence; its 8 warps are 16 half-warps, each holding RH key
+// channels of every column in registers (dk <= 16 * RH): lane & 15 is the column, the half-warp the channel group.
+template <int RH>
 __global__ void __launch_bounds__(DC_THREADS)
 decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ kd, const float* __restrict__ ed,
                         const float* __restrict__ P, const float* __restrict__ v, int ldv, int act,
                         float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                         float* __restrict__ o, int n_heads, int dk, int dv) {
     mv_pdl_begin();
-    constexpr int DKP = 8 * R;
+    constexpr int DKP = 16 * RH;
     extern __shared__ __align__(16) float smem[];
     float* qt = smem;                               // [DC_CHUNK][DKP], zero beyond dk
     float* kt = qt + DC_CHUNK * DKP;
     float* vt = kt + DC_CHUNK * DKP;                // [DC_CHUNK][DC_COLS]
     float* pt = vt + DC_CHUNK * DC_COLS;            // [DC_CHUNK][DC_CHUNK]
     float* et = pt + DC_CHUNK * DC_CHUNK;           // [DKP]
-    float* red = et + DKP;                          // [8][DC_CHUNK][DC_COLS]
+    float* red = et + DKP;                          // [16][DC_CHUNK][DC_COLS]
     const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
-    const int j = tile * DC_COLS + lane;
+    const int tid = threadIdx.x, col = tid & 15, grp = tid >> 4;
+    const int j = tile * DC_COLS + col;
     const int row0 = cu[b], len = cu[b + 1] - row0;
     if (len <= 0) return;
     const int slot = mv_read_slot(slots[b]);
     const int width = n_heads * dk;
     float* srow = state + (((size_t)slot * n_heads + h) * dv + (j < dv ? j : 0)) * dk;
-    float S[R];
+    float S[RH];
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-        const int i = w * R + r;
+    for (int r = 0; r < RH; ++r) {
+        const int i = grp * RH + r;
         S[r] = (j < dv && i < dk) ? srow[i] : 0.f;
     }
     const int n_chunks = (len + DC_CHUNK - 1) / DC_CHUNK;
-    for (int c = 0; c < n_chunks; ++c) {
+    // A chunk's rows are requested into registers while the chunk before is worked on, and go to shared
+    // memory when that one is done: per thread IT values of the decayed q and of the decayed k, 2 of v, 4 of P
+    // and at most one of the chunk's total decay.
+    constexpr int IT = DC_CHUNK * DKP / DC_THREADS;
+    float rq[IT], rk[IT], rv[DC_CHUNK * DC_COLS / DC_THREADS], rp[DC_CHUNK * DC_CHUNK / DC_THREADS], re = 0.f;
+    auto request = [&](int c) {
         const int nt = min(DC_CHUNK, len - c * DC_CHUNK);
         const int first = row0 + c * DC_CHUNK;
         const int chunk = row0 / DC_CHUNK + b + c;
-        __syncthreads();
-        for (int idx = tid; idx < DC_CHUNK * DKP; idx += DC_THREADS) {
-            const int t = idx / DKP, i = idx - t * DKP;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int idx = tid + it * DC_THREADS, t = idx / DKP, i = idx - t * DKP;
             const bool in = t < nt && i < dk;
-            const size_t at = (size_t)(first + t) * width + (size_t)h * dk + i;
-            qt[idx] = in ? qd[at] : 0.f;
-            kt[idx] = in ? kd[at] : 0.f;
+            const size_t at = in ? (size_t)(first + t) * width + (size_t)h * dk + i : 0;
+            rq[it] = in ? qd[at] : 0.f;
+            rk[it] = in ? kd[at] : 0.f;
         }
-        for (int idx = tid; idx < DC_CHUNK * DC_COLS; idx += DC_THREADS) {
-            const int t = idx / DC_COLS, col = tile * DC_COLS + (idx - t * DC_COLS);
-            float vv = (t < nt && col < dv) ? v[(size_t)(first + t) * ldv + (size_t)h * dv + col] : 0.f;
-            vt[idx] = act ? ds_silu(vv) : vv;
+#pragma unroll
+        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_THREADS; ++it) {
+            const int idx = tid + it * DC_THREADS, t = idx / DC_COLS, cc = tile * DC_COLS + (idx - t * DC_COLS);
+            const float vv = (t < nt && cc < dv) ? v[(size_t)(first + t) * ldv + (size_t)h * dv + cc] : 0.f;
+            rv[it] = act ? ds_silu(vv) : vv;
         }
         const float* Pc = P + ((size_t)chunk * n_heads + h) * DC_CHUNK * DC_CHUNK;
-        for (int idx = tid; idx < DC_CHUNK * DC_CHUNK; idx += DC_THREADS) pt[idx] = Pc[idx];
-        for (int i = tid; i < DKP; i += DC_THREADS) et[i] = i < dk ? ed[(size_t)chunk * width + (size_t)h * dk + i] : 0.f;
+#pragma unroll
+        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_THREADS; ++it) rp[it] = Pc[tid + it * DC_THREADS];
+        if (tid < DKP) re = tid < dk ? ed[(size_t)chunk * width + (size_t)h * dk + tid] : 0.f;
+    };
+    request(0);
+    for (int c = 0; c < n_chunks; ++c) {
+        const int nt = min(DC_CHUNK, len - c * DC_CHUNK);
+        const int first = row0 + c * DC_CHUNK;
+        __syncthreads();                            // the chunk before is done with shared memory
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            qt[tid + it * DC_THREADS] = rq[it];
+            kt[tid + it * DC_THREADS] = rk[it];
+        }
+#pragma unroll
+        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_THREADS; ++it) vt[tid + it * DC_THREADS] = rv[it];
+#pragma unroll
+        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_THREADS; ++it) pt[tid + it * DC_THREADS] = rp[it];
+        if (tid < DKP) et[tid] = re;
         __syncthreads();
-        // what the chunk's tokens read from the state before the chunk: this warp's key channels
+        if (c + 1 < n_chunks) request(c + 1);
+        // what the chunk's tokens read from the state before the chunk: this half-warp's key channels
 #pragma unroll 4
         for (int t = 0; t < DC_CHUNK; ++t) {
-            const float4* q4 = reinterpret_cast<const float4*>(qt + t * DKP + w * R);
+            const float4* q4 = reinterpret_cast<const float4*>(qt + t * DKP + grp * RH);
             float acc = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; r += 4) {
+            for (int r = 0; r < RH; r += 4) {
                 const float4 x = q4[r >> 2];
                 acc = fmaf(x.x, S[r], acc); acc = fmaf(x.y, S[r + 1], acc);
                 acc = fmaf(x.z, S[r + 2], acc); acc = fmaf(x.w, S[r + 3], acc);
             }
-            red[(w * DC_CHUNK + t) * DC_COLS + lane] = acc;
+            red[(grp * DC_CHUNK + t) * DC_COLS + col] = acc;
         }
         // the state after the chunk
 #pragma unroll
-        for (int r = 0; r < R; ++r) S[r] *= et[w * R + r];
-#pragma unroll 2
+        for (int r = 0; r < RH; ++r) S[r] *= et[grp * RH + r];
+#pragma unroll 4
         for (int s = 0; s < DC_CHUNK; ++s) {
-            const float vj = vt[s * DC_COLS + lane];
-            const float4* k4 = reinterpret_cast<const float4*>(kt + s * DKP + w * R);
+            const float vj = vt[s * DC_COLS + col];
+            const float4* k4 = reinterpret_cast<const float4*>(kt + s * DKP + grp * RH);
 #pragma unroll
-            for (int r = 0; r < R; r += 4) {
+            for (int r = 0; r < RH; r += 4) {
                 const float4 x = k4[r >> 2];
                 S[r] = fmaf(x.x, vj, S[r]); S[r + 1] = fmaf(x.y, vj, S[r + 1]);
                 S[r + 2] = fmaf(x.z, vj, S[r + 2]); S[r + 3] = fmaf(x.w, vj, S[r + 3]);
             }
         }
         __syncthreads();
-        // outputs: the eight warps' shares in a fixed order, then the chunk's own tokens
-        for (int t = w; t < nt; t += 8) {
+        // outputs: the sixteen groups' shares in a fixed order, then the chunk's own tokens
+        for (int idx = tid; idx < nt * DC_COLS; idx += DC_THREADS) {
+            const int t = idx / DC_COLS, cc = idx - t * DC_COLS;
             float sum = 0.f;
 #pragma unroll
-            for (int ww = 0; ww < 8; ++ww) sum += red[(ww * DC_CHUNK + t) * DC_COLS + lane];
-            for (int s = 0; s <= t; ++s) sum = fmaf(pt[t * DC_CHUNK + s], vt[s * DC_COLS + lane], sum);
-            if (j < dv) o[(size_t)(first + t) * n_heads * dv + (size_t)h * dv + j] = sum;
+            for (int g = 0; g < 16; ++g) sum += red[(g * DC_CHUNK + t) * DC_COLS + cc];
+            for (int s = 0; s <= t; ++s) sum = fmaf(pt[t * DC_CHUNK + s], vt[s * DC_COLS + cc], sum);
+            if (tile * DC_COLS + cc < dv) o[(size_t)(first + t) * n_heads * dv + (size_t)h * dv + tile * DC_COLS + cc] = sum;
         }
     }
     if (j < dv && mv_slot_ok(slots[b])) {
 #pragma unroll
-        for (int r = 0; r < R; ++r) {
-            const int i = w * R + r;
+        for (int r = 0; r < RH; ++r) {
+            const int i = grp * RH + r;
             if (i < dk) srow[i] = S[r];
         }
     }
 }
 
-template <int R>
+template <int RH>
 static int decay_chunk_scan_launch(dim3 grid, cudaStream_t stream, const float* qd, const float* kd, const float* ed,
                                    const float* P, const float* v, int ldv, int act, float* state, const int* slots,
                                    const int* cu, float* o, int n_heads, int dk, int dv) {
-    const size_t smem = sizeof(float) * ((size_t)2 * DC_CHUNK * 8 * R + DC_CHUNK * DC_COLS + DC_CHUNK * DC_CHUNK + 8 * R +
-                                         8 * DC_CHUNK * DC_COLS);
+    const size_t smem = sizeof(float) * ((size_t)2 * DC_CHUNK * 16 * RH + DC_CHUNK * DC_COLS + DC_CHUNK * DC_CHUNK + 16 * RH +
+                                         16 * DC_CHUNK * DC_COLS);
     static bool attr_set = false;
     if (!attr_set) {
-        cudaFuncSetAttribute(decay_chunk_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(decay_chunk_scan_kernel<RH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    mv_launch(decay_chunk_scan_kernel<R>, grid, DC_THREADS, smem, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o,
+    mv_launch(decay_chunk_scan_kernel<RH>, grid, DC_THREADS, smem, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o,
               n_heads, dk, dv);
     return mv_launch_status();
 }
@@ -342,7 +369,7 @@ MV_API int mv_decay_scan_chunked(const float* q, int ldq, const float* k, int ld
     int code = mv_launch_status();
     if (code) return code;
     const dim3 grid((dv + DC_COLS - 1) / DC_COLS, n_heads, n_seqs);
-    if (dk <= 64) return decay_chunk_scan_launch<8>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
-    if (dk <= 128) return decay_chunk_scan_launch<16>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
-    return decay_chunk_scan_launch<32>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    if (dk <= 64) return decay_chunk_scan_launch<4>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    if (dk <= 128) return decay_chunk_scan_launch<8>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    return decay_chunk_scan_launch<16>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
 }

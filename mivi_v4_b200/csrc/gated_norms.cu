@@ -70,11 +70,44 @@ gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gate
     }
 }
 
+// The same with one block per (row, group), for groups of many values (a norm over all heads of a wide layer).
+template <typename TO>
+__global__ void __launch_bounds__(256)
+gated_rmsnorm_block_kernel(const float* __restrict__ x, const float* __restrict__ gate, int ld_gate,
+                           const float* __restrict__ w, int w_len, TO* __restrict__ y, int C, int group, float eps,
+                           int act) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const int per_row = C / group;
+    const long long n = blockIdx.x / per_row;
+    const int c0 = (int)(blockIdx.x - n * per_row) * group;
+    const float* xr = x + (size_t)n * C + c0;
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < group; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)group + eps);
+    const float* gr = gate + (size_t)n * ld_gate + c0;
+    TO* yr = y + (size_t)n * C + c0;
+    for (int d = threadIdx.x; d < group; d += blockDim.x) {
+        const float g = gr[d];
+        const float sg = 1.0f / (1.0f + expf(-g));
+        yr[d] = mv_from_f32<TO>(xr[d] * scale * w[(c0 + d) % w_len] * (act == 0 ? g * sg : sg));
+    }
+}
+
 MV_API int mv_gated_rmsnorm(const float* x, const float* gate, int ld_gate, const float* w, int w_len, void* y,
                             int y_dtype, int N, int C, int group, float eps, int act, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (group < 1 || C % group || w_len < 1) return (int)cudaErrorInvalidValue;
     const long long n_groups = (long long)N * (C / group);
+    if (group >= 512) {
+        if (y_dtype == MV_DT_BF16)
+            mv_launch(gated_rmsnorm_block_kernel<__nv_bfloat16>, (unsigned)n_groups, 256, 0, stream, x, gate, ld_gate, w,
+                      w_len, (__nv_bfloat16*)y, C, group, eps, act);
+        else
+            mv_launch(gated_rmsnorm_block_kernel<float>, (unsigned)n_groups, 256, 0, stream, x, gate, ld_gate, w, w_len,
+                      (float*)y, C, group, eps, act);
+        return mv_launch_status();
+    }
     const unsigned blocks = (unsigned)((n_groups + 7) / 8);
     if (y_dtype == MV_DT_BF16)
         mv_launch(gated_rmsnorm_kernel<__nv_bfloat16>, blocks, 256, 0, stream, x, gate, ld_gate, w, w_len,
