@@ -165,7 +165,9 @@ decay_chunk_prepare_kernel(const float* __restrict__ q, int ldq, const float* __
     const int first = row0 + c * DC_CHUNK;
     const int chunk = row0 / DC_CHUNK + b + c;
     const int tid = threadIdx.x;
-    const float log_hd = head_decay ? logf(head_decay[h]) : 0.f;
+    // a decay of exactly 0 has no logarithm; e^-80 stands in for it (what is left of the state then lies 35
+    // decimal places down)
+    const float log_hd = head_decay ? fmaxf(logf(head_decay[h]), -80.f) : 0.f;
     for (int idx = tid; idx < nt * dk; idx += DC_THREADS) {
         const int t = idx / dk, i = idx - t * dk;
         const size_t row = (size_t)(first + t);

@@ -219,3 +219,49 @@ MV_API int mv_round_rows(const float* x, void* out, int out_dtype, long long tot
         mv_launch(round_rows_kernel<float>, blocks, 256, 0, stream, x, (float*)out, total);
     return mv_launch_status();
 }
+
+// ------------------------------------- a narrow projection of the residual stream, gated by a table row
+// out[n, d] = gelu_tanh(G[d, :] . x) * table[tokens[n], col0 + d] with x = resid[n, :] rounded to the matrix's
+// type: ``round_rows``, the product with G [D, H] and ``table_gate`` in one kernel, for steps of few tokens
+// (every block reads its rows of G once a token).  One warp per (token, d); sums in float32.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+table_gate_proj_kernel(const float* __restrict__ resid, const TW* __restrict__ G, const TW* __restrict__ table,
+                       int ld_table, int col0, const int* __restrict__ tokens, TO* __restrict__ out, int N, int H, int D) {
+    mv_pdl_begin();
+    const int lane = threadIdx.x & 31;
+    const int d = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5), n = blockIdx.x;
+    if (d >= D) return;
+    const float* x = resid + (size_t)n * H;
+    const TW* g = G + (size_t)d * H;
+    float dot = 0.f;
+    if (H % 8 == 0 && (((uintptr_t)g | (uintptr_t)x) & 31) == 0) {
+        for (int h = lane * 8; h < H; h += 256) {
+            float gv[8], xv[8];
+            mv_load8(g + h, gv);
+            mv_load8(x + h, xv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) dot = fmaf(mv_to_f32(mv_from_f32<TW>(xv[e])), gv[e], dot);
+        }
+    } else {
+        for (int h = lane; h < H; h += 32) dot = fmaf(mv_to_f32(mv_from_f32<TW>(x[h])), mv_to_f32(g[h]), dot);
+    }
+    dot = mv_warp_sum(dot);
+    if (lane == 0) {
+        const float gelu = 0.5f * dot * (1.0f + tanhf(0.7978845608028654f * (dot + 0.044715f * dot * dot * dot)));
+        out[(size_t)n * D + d] = mv_from_f32<TO>(gelu * mv_to_f32(table[(size_t)tokens[n] * ld_table + col0 + d]));
+    }
+}
+
+MV_API int mv_table_gate_proj(const float* resid, const void* G, const void* table, int dtype, int ld_table, int col0,
+                              const int* tokens, void* out, int N, int H, int D, cudaStream_t stream) {
+    if (N <= 0 || D <= 0) return 0;
+    const dim3 grid(N, (D + 7) / 8);
+    if (dtype == MV_DT_BF16)
+        mv_launch(table_gate_proj_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, resid,
+                  (const __nv_bfloat16*)G, (const __nv_bfloat16*)table, ld_table, col0, tokens, (__nv_bfloat16*)out, N, H, D);
+    else
+        mv_launch(table_gate_proj_kernel<float, float>, grid, 256, 0, stream, resid, (const float*)G, (const float*)table,
+                  ld_table, col0, tokens, (float*)out, N, H, D);
+    return mv_launch_status();
+}

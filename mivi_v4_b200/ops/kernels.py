@@ -50,6 +50,7 @@ _SIGNATURES = {
         "mv_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _P],
         "mv_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
         "mv_table_gate": [_P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
+        "mv_table_gate_proj": [_P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
         "mv_round_rows": [_P, _P, _I, _Q, _P],
         "mv_decay_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _F, _F, _I, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "mv_decay_chunks": [_I, _I],
@@ -420,6 +421,34 @@ def table_gate(p: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Te
         int(col0), _need(tokens, "tokens", torch.int32), _need(out, "table_gate out", None, (N, D)), _dt(out), N, D,
         _stream()), "mv_table_gate")
     account(_nbytes(p, out) + N * D * table.element_size())
+    return out
+
+
+TABLE_GATE_PROJ_MAX_ROWS = 64
+
+
+def table_gate_proj_ok(n_rows: int, gate: torch.Tensor, table: torch.Tensor, dtype: torch.dtype) -> bool:
+    """Whether ``table_gate_proj`` takes a step: few rows (every token re-reads the matrix), matrix and table in
+    the run's dtype."""
+    return 1 <= n_rows <= TABLE_GATE_PROJ_MAX_ROWS and gate.dtype == table.dtype == dtype
+
+
+def table_gate_proj(resid: torch.Tensor, gate: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor,
+                    out: torch.Tensor) -> torch.Tensor:
+    """out[n, d] = gelu_tanh(gate[d] . x_n) * table[tokens[n], col0 + d], x_n being row n of ``resid`` (float32)
+    rounded to the matrix's dtype: ``round_rows``, a product and ``table_gate`` in one kernel, for few rows."""
+    N, H = resid.shape
+    D = gate.shape[0]
+    if not table_gate_proj_ok(N, gate, table, out.dtype):
+        raise KernelError("table_gate_proj: too many rows or mixed dtypes; ask table_gate_proj_ok first")
+    if gate.shape[1] != H or col0 < 0 or col0 + D > table.shape[1]:
+        raise KernelError(f"table_gate_proj: gate {tuple(gate.shape)} and columns {col0}..{col0 + D} of a table "
+                          f"{tuple(table.shape)} do not fit rows of {H}")
+    _check(_fn("core", "mv_table_gate_proj")(
+        _need(resid, "residual stream", torch.float32), _need(gate, "gate matrix"), _need(table, "table"), _dt(gate),
+        table.shape[1], int(col0), _need(tokens, "tokens", torch.int32), _need(out, "table_gate_proj out", None, (N, D)),
+        N, H, D, _stream()), "mv_table_gate_proj")
+    account(N * (H * D * gate.element_size() + 4 * H), 2 * N * H * D)
     return out
 
 

@@ -37,13 +37,17 @@ class GatedTableInput(Part):
 
     def forward(self, resid, step) -> None:
         N, H = resid.shape
-        x = resid
-        if step.dtype != torch.float32:
-            x = K.round_rows(resid, self.scratch(step, "x", (N, H), step.dtype))
-        p = self.scratch(step, "p", (N, self.dim), torch.float32)
-        linear(x, self.w_gate, p)
         g = self.scratch(step, "g", (N, self.dim), step.dtype)
-        K.table_gate(p, self.table, self.index * self.dim, step.tokens, g)
+        if K.table_gate_proj_ok(N, self.w_gate, self.table, step.dtype):
+            # a few tokens: rounding, the narrow product and the gate in one kernel
+            K.table_gate_proj(resid, self.w_gate, self.table, self.index * self.dim, step.tokens, g)
+        else:
+            x = resid
+            if step.dtype != torch.float32:
+                x = K.round_rows(resid, self.scratch(step, "x", (N, H), step.dtype))
+            p = self.scratch(step, "p", (N, self.dim), torch.float32)
+            linear(x, self.w_gate, p)
+            K.table_gate(p, self.table, self.index * self.dim, step.tokens, g)
         y = self.scratch(step, "y", (N, H), torch.float32)
         linear(g, self.w_proj, y)
         K.rmsnorm_add(y, self.norm, self.eps, resid)

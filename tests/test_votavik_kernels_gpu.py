@@ -78,6 +78,23 @@ def test_rmsnorm_add_glu_table_gate_round():
     assert torch.equal(r, y.to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("H,D", [(72, 5), (256, 64), (1001, 24)])
+def test_table_gate_proj_in_one_kernel(H, D, dtype):
+    torch.manual_seed(H + D)
+    N, V, col0 = 7, 50, 2 * D
+    resid = torch.randn(N, H).to(DEV)
+    gate = (torch.randn(D, H) / H ** 0.5).to(dtype).to(DEV)
+    table = torch.randn(V, 4 * D).to(dtype).to(DEV)
+    toks = torch.tensor([0, 49, 7, 7, 13, 1, 30], dtype=torch.int32, device=DEV)
+    x = resid.cpu().to(dtype).double()
+    want = P.gelu_tanh(x @ gate.double().cpu().T) * table.double().cpu()[toks.long().cpu(), col0:col0 + D]
+    out = torch.full((N, D), float("nan"), dtype=dtype, device=DEV)
+    assert K.table_gate_proj_ok(N, gate, table, dtype)
+    K.table_gate_proj(resid, gate, table, col0, toks, out)
+    close(out, want, dtype)
+
+
 def _scan_case(N, heads, dk, dv, seed):
     torch.manual_seed(seed)
     wide = torch.randn(N, heads * (2 * dk + dv) + 3).to(DEV)

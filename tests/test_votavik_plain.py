@@ -88,7 +88,7 @@ def test_dense_feed_forward_clamps():
          "f.down": torch.eye(2, dtype=F64)}
     y = P.dense_ff(torch.ones(1, 1, dtype=F64), w, "f.", c)
     # gate 10 -> 1 (capped above only), up 10 -> 1; gate -10 stays, up -10 -> -1 so (u + 1) = 0
-    assert torch.allclose(y[0, 0], torch.tensor(1.0 * torch.sigmoid(torch.tensor(1.702, dtype=F64)) * 2.0))
+    assert torch.allclose(y[0, 0], 2.0 * torch.sigmoid(torch.tensor(1.702, dtype=F64)))
     assert y[0, 1].abs() < 1e-12
 
 
@@ -135,3 +135,40 @@ def test_window_cache_keeps_the_pages_of_the_first_tokens():
     cache.release(s)
     cache.check()
     assert cache.pages[0].free_count == 8
+
+
+def test_command_line_random_then_info_and_a_checkpoint_that_gives_the_rank(tmp_path, capsys):
+    import json
+    from safetensors.torch import load_file
+    from mivi_v4_b200 import WeightsError
+    from mivi_v4_b200.cli import main
+    from mivi_v4_b200.engine.model import expected_tensors
+    from mivi_v4_b200.weights.loader import check_entries
+    from mivi_v4_b200.weights.safetensors_io import read_model_headers
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(VOT_P))
+    out = tmp_path / "model"
+    assert main(["random", "--config", str(cfg), "--seed", "3", "--out", str(out)]) == 0
+    capsys.readouterr()
+    assert main(["info", "-m", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "architecture: Votavik" in text and "side.embed" in text and "l1.mix.a2.b" in text
+    weights = load_file(str(out / "model.safetensors"))
+    assert weights["l1.mix.a1"].shape == (8, 64) and weights["l0.mix.sink"].shape == (6,)
+    # a configuration without the decay's rank takes it from the checkpoint: any rank fits the name table,
+    # but the two projections must still have the declared outer sizes
+    no_rank = json.loads(json.dumps(VOT_P))
+    del no_rank["layers"][1]["mixer"]["rank"]
+    check_entries("the folder", expected_tensors(no_rank), read_model_headers(str(out)))
+    wrong = json.loads(json.dumps(no_rank))
+    wrong["layers"][1]["mixer"]["dim"] = 24
+    with pytest.raises(WeightsError):
+        check_entries("the folder", expected_tensors(wrong), read_model_headers(str(out)))
+    with pytest.raises(ValueError):
+        main(["random", "--config", str(_write(tmp_path / "c2.json", no_rank)), "--out", str(tmp_path / "m2")])
+
+
+def _write(path, cfg):
+    import json
+    path.write_text(json.dumps(cfg))
+    return path
