@@ -110,14 +110,17 @@ MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const
 }
 
 // ------------------------------------------------------------------ attention
-// One block of eight warps per (token, query head).  The keys a query reads are the kept first ones
-// [0, keep) and the window [lo, pos], walked as one run, 32 at a time; the runs are dealt out to the eight
-// warps in turn.  In a run each lane scores one key, the warp agrees on the running maximum, then the
-// lanes split the value's elements for the weighted sum.  The sink starts the first warp's running maximum
-// and denominator (its own term is exp(sink - max)), so it is counted once and needs no key.  The eight
-// partial results are merged in a fixed order, so a position's result depends on nothing but its keys.
+// One block of eight warps per (token, kv head, tile of GT query heads of that kv head): the heads of a group
+// read the same keys and values, so a key row and a value row are loaded once for all of them.  The keys a
+// query reads are the kept first ones [0, keep) and the window [lo, pos], walked as one run, 32 at a time; the
+// runs are dealt out to the eight warps in turn.  In a run each lane scores one key (against every head of the
+// tile), the warp agrees on each head's running maximum, then the lanes split the value's elements for the
+// weighted sums.  The sink starts the first warp's running maximum and denominator (its own term is
+// exp(sink - max)), so it is counted once and needs no key.  The eight partial results are merged in a fixed
+// order, so a position's result depends on nothing but its keys.
 #define AS_WARPS 8
-template <typename T, bool VEC>
+#define AS_ACC (AS_MAX_DIM / 32)
+template <typename T, bool VEC, int GT>
 __global__ void __launch_bounds__(AS_WARPS * 32)
 attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long long page_stride,
                       const int* __restrict__ page_table, int table_stride, int page_shift,
@@ -126,26 +129,36 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
                       T* __restrict__ o, int N, int nh, int nkv, int dk, int dv, float scale, float cap, int window,
                       int keep_first) {
     mv_pdl_begin();
-    __shared__ float qs[AS_MAX_DIM];
-    __shared__ float part_acc[AS_WARPS][AS_MAX_DIM];
-    __shared__ float part_m[AS_WARPS], part_l[AS_WARPS];
+    extern __shared__ __align__(16) float as_smem[];
+    float* qs = as_smem;                            // [GT][dk]
+    float* part_acc = qs + GT * dk;                 // [AS_WARPS][GT][dv]
+    float* part_m = part_acc + AS_WARPS * GT * dv;  // [AS_WARPS][GT]
+    float* part_l = part_m + AS_WARPS * GT;
     const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x / nh, h = blockIdx.x - n * nh;
-    const int g = h / (nh / nkv);
+    const int G = nh / nkv, tiles = (G + GT - 1) / GT;
+    const int n = blockIdx.x / (nkv * tiles), rest = blockIdx.x - n * nkv * tiles;
+    const int g = rest / tiles, h0 = g * G + (rest - g * tiles) * GT;        // the tile's first query head
+    const int n_heads = min(GT, (g + 1) * G - h0);
     const int pos = positions[n];
     const int page_size = 1 << page_shift;
     const int* table = page_table + (size_t)seq_of[n] * table_stride;
     const size_t v_base = (size_t)nkv * page_size * dk;
 
-    const T* qrow = q + ((size_t)n * nh + h) * dk;
-    for (int d = threadIdx.x; d < dk; d += AS_WARPS * 32) qs[d] = mv_to_f32(qrow[d]);
+    for (int idx = threadIdx.x; idx < GT * dk; idx += AS_WARPS * 32) {
+        const int i = idx / dk, d = idx - i * dk;
+        qs[idx] = i < n_heads ? mv_to_f32(q[((size_t)n * nh + h0 + i) * dk + d]) : 0.f;
+    }
     __syncthreads();
 
-    float acc[AS_MAX_DIM / 32];
+    float acc[GT][AS_ACC], m[GT], l[GT];
 #pragma unroll
-    for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] = 0.f;
-    float m = (sinks && wib == 0) ? sinks[h] : -INFINITY;
-    float l = (sinks && wib == 0) ? 1.f : 0.f;
+    for (int i = 0; i < GT; ++i) {
+#pragma unroll
+        for (int r = 0; r < AS_ACC; ++r) acc[i][r] = 0.f;
+        const bool first = sinks && wib == 0 && i < n_heads;
+        m[i] = first ? sinks[h0 + i] : -INFINITY;
+        l[i] = first ? 1.f : 0.f;
+    }
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     const int keep = min(keep_first, lo);
     const int total = keep + (pos - lo + 1);
@@ -155,7 +168,9 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
         const int u = u0 + lane;
         const bool valid = u < total;
         const int t = u < keep ? u : lo + (u - keep);
-        float s = -INFINITY;
+        float s[GT], p[GT];
+#pragma unroll
+        for (int i = 0; i < GT; ++i) s[i] = -INFINITY;
         unsigned long long vaddr = 0;
         if (valid) {
             const int page = mv_read_page(table[t >> page_shift]);
@@ -163,78 +178,111 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
             const size_t r = (size_t)g * page_size + (t & (page_size - 1));
             const T* krow = pbase + r * dk;
             vaddr = (unsigned long long)(pbase + v_base + r * dv);
-            float dot = 0.f;
+            float dot[GT];
+#pragma unroll
+            for (int i = 0; i < GT; ++i) dot[i] = 0.f;
             if (VEC) {
 #pragma unroll 4
                 for (int d = 0; d < dk; d += 8) {
                     float kv[8];
                     mv_load8(krow + d, kv);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) dot = fmaf(qs[d + e], kv[e], dot);
+                    for (int i = 0; i < GT; ++i) {
+                        // dk is a multiple of 8 here: the head's row in shared memory is read four values at a time
+                        const float4 qa = *reinterpret_cast<const float4*>(qs + i * dk + d);
+                        const float4 qb = *reinterpret_cast<const float4*>(qs + i * dk + d + 4);
+                        dot[i] = fmaf(qa.x, kv[0], dot[i]); dot[i] = fmaf(qa.y, kv[1], dot[i]);
+                        dot[i] = fmaf(qa.z, kv[2], dot[i]); dot[i] = fmaf(qa.w, kv[3], dot[i]);
+                        dot[i] = fmaf(qb.x, kv[4], dot[i]); dot[i] = fmaf(qb.y, kv[5], dot[i]);
+                        dot[i] = fmaf(qb.z, kv[6], dot[i]); dot[i] = fmaf(qb.w, kv[7], dot[i]);
+                    }
                 }
             } else {
-                for (int d = 0; d < dk; ++d) dot = fmaf(qs[d], mv_to_f32(krow[d]), dot);
-            }
-            s = dot * scale;
-            if (cap > 0.f) s = cap * tanhf(s * inv_cap);
-        }
-        const float m_new = fmaxf(m, mv_warp_max(s));
-        const float p = valid ? expf(s - m_new) : 0.f;
-        const float corr = m == -INFINITY ? 0.f : expf(m - m_new);
-        l = l * corr + mv_warp_sum(p);
+                for (int d = 0; d < dk; ++d) {
+                    const float kv = mv_to_f32(krow[d]);
 #pragma unroll
-        for (int r = 0; r < AS_MAX_DIM / 32; ++r) acc[r] *= corr;
-        m = m_new;
-        // the values of the run's keys, eight rows requested before any is used (a row whose key is masked or
-        // beyond the run has weight 0 and is not read)
+                    for (int i = 0; i < GT; ++i) dot[i] = fmaf(qs[i * dk + d], kv, dot[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < GT; ++i) {
+                s[i] = dot[i] * scale;
+                if (cap > 0.f) {
+                    if (sizeof(T) == 2) {
+                        // a bfloat16 run: tanh(x) = (1 - e^-2|x|) / (1 + e^-2|x|) with the fast exponential, as in the
+                        // kernel of long steps (within 1e-6 of the cap; the operands were rounded to 2^-9)
+                        const float x = s[i] * inv_cap, e2 = __expf(-2.0f * fabsf(x));
+                        s[i] = copysignf(cap * __fdividef(1.0f - e2, 1.0f + e2), x);
+                    } else {
+                        s[i] = cap * tanhf(s[i] * inv_cap);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < GT; ++i) {
+            const float m_new = fmaxf(m[i], mv_warp_max(s[i]));
+            p[i] = valid ? expf(s[i] - m_new) : 0.f;
+            const float corr = m[i] == -INFINITY ? 0.f : expf(m[i] - m_new);
+            l[i] = l[i] * corr + mv_warp_sum(p[i]);
+#pragma unroll
+            for (int r = 0; r < AS_ACC; ++r) acc[i][r] *= corr;
+            m[i] = m_new;
+        }
+        // the values of the run's keys, eight rows requested before any is used (a row beyond the run is not read)
         const int cnt = min(32, total - u0);
         for (int j0 = 0; j0 < cnt; j0 += 8) {
-            float pj[8];
             const T* vrow[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                pj[e] = __shfl_sync(0xffffffffu, p, j0 + e);
-                vrow[e] = (const T*)__shfl_sync(0xffffffffu, vaddr, j0 + e);
-            }
+            for (int e = 0; e < 8; ++e) vrow[e] = (const T*)__shfl_sync(0xffffffffu, vaddr, j0 + e);
+            float pj[GT][8];
 #pragma unroll
-            for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
+            for (int i = 0; i < GT; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) pj[i][e] = __shfl_sync(0xffffffffu, p[i], j0 + e);
+#pragma unroll
+            for (int r = 0; r < AS_ACC; ++r) {
                 const int d = lane + 32 * r;
                 if (d < dv) {
                     float x[8];
 #pragma unroll
                     for (int e = 0; e < 8; ++e) x[e] = (j0 + e < cnt) ? mv_to_f32(vrow[e][d]) : 0.f;
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[r] = fmaf(pj[e], x[e], acc[r]);
+                    for (int i = 0; i < GT; ++i)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[i][r] = fmaf(pj[i][e], x[e], acc[i][r]);
                 }
             }
         }
     }
-    // merge the warps' partial results: warp 0 always has a finite maximum or a key (the query's own
-    // key lies in some warp's run; with no sink a warp that saw no key holds m = -inf and weighs nothing)
-    if (lane == 0) { part_m[wib] = m; part_l[wib] = l; }
+    // merge the warps' partial results (with no sink a warp that saw no key holds m = -inf and weighs nothing;
+    // the query's own key lies in some warp's run, so a head's denominator is never empty)
 #pragma unroll
-    for (int r = 0; r < AS_MAX_DIM / 32; ++r) {
-        const int d = lane + 32 * r;
-        if (d < dv) part_acc[wib][d] = acc[r];
+    for (int i = 0; i < GT; ++i) {
+        if (lane == 0) { part_m[wib * GT + i] = m[i]; part_l[wib * GT + i] = l[i]; }
+#pragma unroll
+        for (int r = 0; r < AS_ACC; ++r) {
+            const int d = lane + 32 * r;
+            if (d < dv) part_acc[(wib * GT + i) * dv + d] = acc[i][r];
+        }
     }
     __syncthreads();
-    float M = part_m[0];
+    for (int idx = threadIdx.x; idx < n_heads * dv; idx += AS_WARPS * 32) {
+        const int i = idx / dv, d = idx - i * dv;
+        float M = part_m[i];
 #pragma unroll
-    for (int w = 1; w < AS_WARPS; ++w) M = fmaxf(M, part_m[w]);
-    float L = 0.f, wgt[AS_WARPS];
+        for (int w = 1; w < AS_WARPS; ++w) M = fmaxf(M, part_m[w * GT + i]);
+        float L = 0.f, v = 0.f;
 #pragma unroll
-    for (int w = 0; w < AS_WARPS; ++w) {
-        wgt[w] = part_m[w] == -INFINITY ? 0.f : expf(part_m[w] - M);
-        L = fmaf(part_l[w], wgt[w], L);
-    }
-    float mul = 1.0f / L;
-    if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h]));
-    T* orow = o + ((size_t)n * nh + h) * dv;
-    for (int d = threadIdx.x; d < dv; d += AS_WARPS * 32) {
-        float v = 0.f;
-#pragma unroll
-        for (int w = 0; w < AS_WARPS; ++w) v = fmaf(part_acc[w][d], wgt[w], v);
-        orow[d] = mv_from_f32<T>(v * mul);
+        for (int w = 0; w < AS_WARPS; ++w) {
+            const float pm = part_m[w * GT + i];
+            const float wgt = pm == -INFINITY ? 0.f : expf(pm - M);
+            L = fmaf(part_l[w * GT + i], wgt, L);
+            v = fmaf(part_acc[(w * GT + i) * dv + d], wgt, v);
+        }
+        float mul = 1.0f / L;
+        if (gate) mul *= 1.0f / (1.0f + expf(-gate[(size_t)n * ld_gate + h0 + i]));
+        o[((size_t)n * nh + h0 + i) * dv + d] = mv_from_f32<T>(v * mul);
     }
 }
 
@@ -249,18 +297,28 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
-    const unsigned blocks = (unsigned)((long long)N * nh);
+    const int G = nh / nkv;
+    // the heads of a kv head share a block (their keys and values are loaded once) when the step has blocks
+    // enough to fill the device without that; a step of few tokens gives every head a block of its own
+    const int gt = (long long)N * nh < 1024 ? 1 : (G >= 4 ? 4 : (G >= 2 ? 2 : 1));
+    const unsigned blocks = (unsigned)((long long)N * nkv * ((G + gt - 1) / gt));
     const int esize = dtype == MV_DT_BF16 ? 2 : 4;
     const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;
-#define AS_LAUNCH(T, V)                                                                                              \
-    mv_launch(attention_sink_kernel<T, V>, blocks, AS_WARPS * 32, 0, stream, (const T*)q, (const T*)pool, page_stride,          \
-              page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N, nh, nkv, dk,  \
-              dv, scale, cap, window, keep_first)
+    const size_t smem = sizeof(float) * ((size_t)gt * dk + (size_t)AS_WARPS * gt * (dv + 2));
+#define AS_LAUNCH(T, V, GTV)                                                                                         \
+    mv_launch(attention_sink_kernel<T, V, GTV>, blocks, AS_WARPS * 32, smem, stream, (const T*)q, (const T*)pool,    \
+              page_stride, page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N,  \
+              nh, nkv, dk, dv, scale, cap, window, keep_first)
+#define AS_PICK(T, V)                                                                                                \
+    do {                                                                                                             \
+        if (gt == 4) AS_LAUNCH(T, V, 4); else if (gt == 2) AS_LAUNCH(T, V, 2); else AS_LAUNCH(T, V, 1);             \
+    } while (0)
     if (dtype == MV_DT_BF16) {
-        if (vec) AS_LAUNCH(__nv_bfloat16, true); else AS_LAUNCH(__nv_bfloat16, false);
+        if (vec) AS_PICK(__nv_bfloat16, true); else AS_PICK(__nv_bfloat16, false);
     } else {
-        if (vec) AS_LAUNCH(float, true); else AS_LAUNCH(float, false);
+        if (vec) AS_PICK(float, true); else AS_PICK(float, false);
     }
+#undef AS_PICK
 #undef AS_LAUNCH
     return mv_launch_status();
 }
