@@ -286,21 +286,24 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
     }
 }
 
-// q [N, nh * dk]; o [N, nh * dv]; sinks [nh] or null; gate: 32-bit logits, gate[n * ld_gate + h], or null.
+// head_tile: see below.  q [N, nh * dk]; o [N, nh * dv]; sinks [nh] or null; gate: 32-bit logits, gate[n * ld_gate + h], or null.
 MV_API int mv_attention_sink(const void* q, const void* pool, long long page_stride, const int* page_table,
                              int table_stride, int page_size, const int* positions, const int* seq_of,
                              const float* sinks, const float* gate, int ld_gate, void* o, int dtype, int N, int nh,
                              int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-                             cudaStream_t stream) {
+                             int head_tile, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (dk < 1 || dk > AS_MAX_DIM || dv < 1 || dv > AS_MAX_DIM || nkv < 1 || nh % nkv || (page_size & (page_size - 1)))
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
     const int G = nh / nkv;
-    // the heads of a kv head share a block (their keys and values are loaded once) when the step has blocks
-    // enough to fill the device without that; a step of few tokens gives every head a block of its own
-    const int gt = (long long)N * nh < 1024 ? 1 : (G >= 4 ? 4 : (G >= 2 ? 2 : 1));
+    // head_tile query heads of a kv head share a block (their keys and values are loaded once): 1, 2 or 4, or 0
+    // for the kernel's own choice.  Measured at 8 and 64 sequences of 1,088 visible keys (32 heads on 8 kv heads),
+    // a block a head was as fast or faster (more blocks in flight hide the loads' latency; the shared rows
+    // come from L2 anyway), so tiles are chosen only for steps of thousands of (token, head) pairs.
+    int gt = head_tile > 0 ? head_tile : ((long long)N * nh >= 4096 && G >= 2 ? 2 : 1);
+    if (gt != 1 && gt != 2 && gt != 4) return (int)cudaErrorInvalidValue;
     const unsigned blocks = (unsigned)((long long)N * nkv * ((G + gt - 1) / gt));
     const int esize = dtype == MV_DT_BF16 ? 2 : 4;
     const bool vec = dk % 8 == 0 && ((uintptr_t)pool % 16) == 0 && (page_stride * esize) % 16 == 0;

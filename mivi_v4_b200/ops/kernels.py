@@ -58,7 +58,7 @@ _SIGNATURES = {
                                   _I, _I, _I, _P],
         "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_attention_sink": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I,
-                              _P],
+                              _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
@@ -576,12 +576,13 @@ def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optiona
 def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
                    out: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, scale: float, *, softcap: float = 0.0,
                    window: int = 0, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, head_tile: int = 0) -> torch.Tensor:
     """Causal softmax attention of every token of the step over its sequence's cache (which already holds the
     step's own keys), keys of size dk and values of size dv.  ``softcap`` c > 0: s <- c tanh(s / c).  ``window``
     w > 0 with ``keep_first`` f: query i reads key j if i - j < w or j < f.  ``sinks`` [nh]: exp(sink) joins
     each head's denominator.  ``gate``: float32 logits [N, nh] (a column slice is fine); the head's output is
-    multiplied by sigmoid(gate)."""
+    multiplied by sigmoid(gate).  ``head_tile``: how many query heads of a kv head share a block and its loads
+    (1, 2 or 4; 0: the kernel chooses by the step's size)."""
     N = q.shape[0]
     if not (1 <= dk <= MAX_HEAD_DIM and 1 <= dv <= MAX_HEAD_DIM):
         raise KernelError(f"attention_sink: key size {dk} and value size {dv} must lie in 1..{MAX_HEAD_DIM}")
@@ -597,8 +598,8 @@ def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_tab
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
-        _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), _stream()),
-        "mv_attention_sink")
+        _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(head_tile),
+        _stream()), "mv_attention_sink")
     return out
 
 

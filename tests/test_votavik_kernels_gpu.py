@@ -297,6 +297,12 @@ def test_attention_sink_window_edges_far_keys_and_the_sink(nh, nkv, dk, dv, wind
     K.attention_sink(q.reshape(N, -1).to(dtype).to(DEV), pool, ps, table, pos_t, seq_of, out, nh, nkv, dk, dv, scale,
                      softcap=cap, window=window, keep_first=keep, sinks=sinks.to(DEV), gate=gate_wide[:, 2:2 + nh])
     close(out, want, dtype, "with sink and gate")
+    for tile in (1, 2, 4):                                    # query heads of a kv head sharing a block's loads
+        out.fill_(float("nan"))
+        K.attention_sink(q.reshape(N, -1).to(dtype).to(DEV), pool, ps, table, pos_t, seq_of, out, nh, nkv, dk, dv, scale,
+                         softcap=cap, window=window, keep_first=keep, sinks=sinks.to(DEV), gate=gate_wide[:, 2:2 + nh],
+                         head_tile=tile)
+        close(out, want, dtype, f"head tile {tile}")
     # without sink and gate the same keys are read and the weights sum to one
     K.attention_sink(q.reshape(N, -1).to(dtype).to(DEV), pool, ps, table, pos_t, seq_of, out, nh, nkv, dk, dv, scale,
                      softcap=cap, window=window, keep_first=keep)
