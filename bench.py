@@ -200,10 +200,10 @@ DESIGN_SIZES = {
 
 def votavik_config(width, layers, heads, kv_heads, ff, vocab):
     gla = {"type": "gla", "mlp": None,
-           "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 16.0, "rank": 16}}
+           "mixer": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "tau": 8.0, "rank": 16}}
     att = {"type": "attention", "mlp": {"kind": "dense", "ff": ff, "limit": 7.0},
-           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 96, "vdim": 64, "scale": 96 ** -0.5, "softcap": 50.0,
-                     "mask": {"size": 1024, "keep_first": 64}, "rot": {"dims": 64, "base": 10000.0}}}
+           "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": 80, "vdim": 64, "scale": 80 ** -0.5, "softcap": 30.0,
+                     "mask": {"size": 1024, "keep_first": 64}, "rot": {"dims": 32, "base": 10000.0}}}
     n_light = max(1, width // 128)
     lig = {"type": "lightning", "mlp": None,
            "mixer": {"heads": n_light, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 5 * i / n_light) for i in range(n_light)]}}

@@ -45,16 +45,21 @@ VOT_Q = {"architecture": "Votavik", "vocab": 131, "width": 48, "norm": {"eps": 1
          "layers": [_light(1, 20, 20, [0.8]),
                     _gla(1, 20, 20, 1.0, 5),
                     _attn(1, 1, 20, 20, 80, 70, 0, 1.0, 0.3, 5.0, _mlp(56, 0.5)),
-                    _gla(3, 8, 4, 16.0, 16)]}
+                    _gla(3, 8, 4, 12.0, 16)]}
 
 # R: wider heads (keys of 72 and 136: more than 64 and 128 key channels a thread group), a window of one page
 # exactly with a kept first page, every layer with a feed-forward
 VOT_R = {"architecture": "Votavik", "vocab": 200, "width": 128, "norm": {"eps": 1e-6}, "token_side": {"dim": 5},
          "layers": [_gla(2, 72, 40, 8.0, 24),
-                    _attn(4, 1, 32, 64, 64, 64, 16, 500.0, 0.17, 50.0, _mlp(136, 2.0)),
+                    _attn(4, 1, 32, 64, 64, 64, 16, 500.0, 0.17, 40.0, _mlp(136, 2.5)),
                     _light(1, 136, 17, [0.97], _mlp(64, 2.0))]}
 
-CONFIGS = {"P": (VOT_P, 11), "Q": (VOT_Q, 12), "R": (VOT_R, 13)}
+# S: no attention layer at all (a cache without keys and values: states only), a feed-forward on a recurrent layer
+VOT_S = {"architecture": "Votavik", "vocab": 77, "width": 40, "norm": {"eps": 1e-5}, "token_side": {"dim": 16},
+         "layers": [_light(2, 16, 8, [0.9, 0.5], _mlp(48, 4.0)),
+                    _gla(4, 8, 8, 2.0, 8)]}
+
+CONFIGS = {"P": (VOT_P, 11), "Q": (VOT_Q, 12), "R": (VOT_R, 13), "S": (VOT_S, 14)}
 
 
 def sharpen(weights, cfg, seed):
