@@ -145,7 +145,12 @@ MV_API int mv_decay_scan(const float* q, int ldq, const float* k, int ldk, const
 // numbers below N / DC_CHUNK + n_seqs + 1 that need nothing from the host.
 #define DC_CHUNK 32
 #define DC_COLS 16
-#define DC_THREADS 256
+#define DC_THREADS 256            // the preparing kernel
+#define DC_SCAN_THREADS 512       // the scanning kernel: 32 half-warps
+#define DC_GROUPS (DC_SCAN_THREADS / 16)
+// a group's shares of a chunk's outputs, padded by half a row of banks: the two groups of a warp then store into
+// different banks
+#define DC_RED_STRIDE (DC_CHUNK * DC_COLS + 16)
 
 __global__ void __launch_bounds__(DC_THREADS)
 decay_chunk_prepare_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
@@ -203,29 +208,35 @@ decay_chunk_prepare_kernel(const float* __restrict__ q, int ldq, const float* __
             const float* cq = cs + s * lds;
             const float* qt = qa + t * lds;
             const float* kt = ka + s * lds;
-            for (int i = 0; i < dk; ++i) sum = fmaf(qt[i] * kt[i], expf(ct[i] - cq[i]), sum);
+            if (z) {
+                for (int i = 0; i < dk; ++i) sum = fmaf(qt[i] * kt[i], expf(ct[i] - cq[i]), sum);
+            } else {
+                // one decay for all of the head's channels: its power is a factor of the whole sum
+                for (int i = 0; i < dk; ++i) sum = fmaf(qt[i], kt[i], sum);
+                sum *= expf(ct[0] - cq[0]);
+            }
         }
         Pc[p] = sum;
     }
 }
 
-// A block is 16 value columns of one head of one sequence; its 8 warps are 16 half-warps, each holding RH key
-// channels of every column in registers (dk <= 16 * RH): lane & 15 is the column, the half-warp the channel group.
+// A block is 16 value columns of one head of one sequence; its 16 warps are 32 half-warps, each holding RH key
+// channels of every column in registers (dk <= 32 * RH): lane & 15 is the column, the half-warp the channel group.
 template <int RH>
-__global__ void __launch_bounds__(DC_THREADS)
+__global__ void __launch_bounds__(DC_SCAN_THREADS)
 decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ kd, const float* __restrict__ ed,
                         const float* __restrict__ P, const float* __restrict__ v, int ldv, int act,
                         float* __restrict__ state, const int* __restrict__ slots, const int* __restrict__ cu,
                         float* __restrict__ o, int n_heads, int dk, int dv) {
     mv_pdl_begin();
-    constexpr int DKP = 16 * RH;
+    constexpr int DKP = DC_GROUPS * RH;
     extern __shared__ __align__(16) float smem[];
     float* qt = smem;                               // [DC_CHUNK][DKP], zero beyond dk
     float* kt = qt + DC_CHUNK * DKP;
     float* vt = kt + DC_CHUNK * DKP;                // [DC_CHUNK][DC_COLS]
     float* pt = vt + DC_CHUNK * DC_COLS;            // [DC_CHUNK][DC_CHUNK]
     float* et = pt + DC_CHUNK * DC_CHUNK;           // [DKP]
-    float* red = et + DKP;                          // [16][DC_CHUNK][DC_COLS]
+    float* red = et + DKP;                          // [DC_GROUPS][DC_RED_STRIDE]: [DC_CHUNK][DC_COLS] a group
     const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, col = tid & 15, grp = tid >> 4;
     const int j = tile * DC_COLS + col;
@@ -244,29 +255,31 @@ decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ 
     // A chunk's rows are requested into registers while the chunk before is worked on, and go to shared
     // memory when that one is done: per thread IT values of the decayed q and of the decayed k, 2 of v, 4 of P
     // and at most one of the chunk's total decay.
-    constexpr int IT = DC_CHUNK * DKP / DC_THREADS;
-    float rq[IT], rk[IT], rv[DC_CHUNK * DC_COLS / DC_THREADS], rp[DC_CHUNK * DC_CHUNK / DC_THREADS], re = 0.f;
+    constexpr int IT = DC_CHUNK * DKP / DC_SCAN_THREADS;
+    static_assert(DC_CHUNK * DC_COLS == DC_SCAN_THREADS && DC_CHUNK * DC_CHUNK % DC_SCAN_THREADS == 0 && DKP <= DC_SCAN_THREADS,
+                  "a thread requests one value of v, whole rounds of P and at most one of the total decay");
+    float rq[IT], rk[IT], rv[DC_CHUNK * DC_COLS / DC_SCAN_THREADS], rp[DC_CHUNK * DC_CHUNK / DC_SCAN_THREADS], re = 0.f;
     auto request = [&](int c) {
         const int nt = min(DC_CHUNK, len - c * DC_CHUNK);
         const int first = row0 + c * DC_CHUNK;
         const int chunk = row0 / DC_CHUNK + b + c;
 #pragma unroll
         for (int it = 0; it < IT; ++it) {
-            const int idx = tid + it * DC_THREADS, t = idx / DKP, i = idx - t * DKP;
+            const int idx = tid + it * DC_SCAN_THREADS, t = idx / DKP, i = idx - t * DKP;
             const bool in = t < nt && i < dk;
             const size_t at = in ? (size_t)(first + t) * width + (size_t)h * dk + i : 0;
             rq[it] = in ? qd[at] : 0.f;
             rk[it] = in ? kd[at] : 0.f;
         }
 #pragma unroll
-        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_THREADS; ++it) {
-            const int idx = tid + it * DC_THREADS, t = idx / DC_COLS, cc = tile * DC_COLS + (idx - t * DC_COLS);
+        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_SCAN_THREADS; ++it) {
+            const int idx = tid + it * DC_SCAN_THREADS, t = idx / DC_COLS, cc = tile * DC_COLS + (idx - t * DC_COLS);
             const float vv = (t < nt && cc < dv) ? v[(size_t)(first + t) * ldv + (size_t)h * dv + cc] : 0.f;
             rv[it] = act ? ds_silu(vv) : vv;
         }
         const float* Pc = P + ((size_t)chunk * n_heads + h) * DC_CHUNK * DC_CHUNK;
 #pragma unroll
-        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_THREADS; ++it) rp[it] = Pc[tid + it * DC_THREADS];
+        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_SCAN_THREADS; ++it) rp[it] = Pc[tid + it * DC_SCAN_THREADS];
         if (tid < DKP) re = tid < dk ? ed[(size_t)chunk * width + (size_t)h * dk + tid] : 0.f;
     };
     request(0);
@@ -276,13 +289,13 @@ decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ 
         __syncthreads();                            // the chunk before is done with shared memory
 #pragma unroll
         for (int it = 0; it < IT; ++it) {
-            qt[tid + it * DC_THREADS] = rq[it];
-            kt[tid + it * DC_THREADS] = rk[it];
+            qt[tid + it * DC_SCAN_THREADS] = rq[it];
+            kt[tid + it * DC_SCAN_THREADS] = rk[it];
         }
 #pragma unroll
-        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_THREADS; ++it) vt[tid + it * DC_THREADS] = rv[it];
+        for (int it = 0; it < DC_CHUNK * DC_COLS / DC_SCAN_THREADS; ++it) vt[tid + it * DC_SCAN_THREADS] = rv[it];
 #pragma unroll
-        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_THREADS; ++it) pt[tid + it * DC_THREADS] = rp[it];
+        for (int it = 0; it < DC_CHUNK * DC_CHUNK / DC_SCAN_THREADS; ++it) pt[tid + it * DC_SCAN_THREADS] = rp[it];
         if (tid < DKP) et[tid] = re;
         __syncthreads();
         if (c + 1 < n_chunks) request(c + 1);
@@ -297,7 +310,7 @@ decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ 
                 acc = fmaf(x.x, S[r], acc); acc = fmaf(x.y, S[r + 1], acc);
                 acc = fmaf(x.z, S[r + 2], acc); acc = fmaf(x.w, S[r + 3], acc);
             }
-            red[(grp * DC_CHUNK + t) * DC_COLS + col] = acc;
+            red[grp * DC_RED_STRIDE + t * DC_COLS + col] = acc;
         }
         // the state after the chunk
 #pragma unroll
@@ -314,12 +327,12 @@ decay_chunk_scan_kernel(const float* __restrict__ qd, const float* __restrict__ 
             }
         }
         __syncthreads();
-        // outputs: the sixteen groups' shares in a fixed order, then the chunk's own tokens
-        for (int idx = tid; idx < nt * DC_COLS; idx += DC_THREADS) {
+        // outputs: the groups' shares in a fixed order, then the chunk's own tokens
+        for (int idx = tid; idx < nt * DC_COLS; idx += DC_SCAN_THREADS) {
             const int t = idx / DC_COLS, cc = idx - t * DC_COLS;
             float sum = 0.f;
 #pragma unroll
-            for (int g = 0; g < 16; ++g) sum += red[(g * DC_CHUNK + t) * DC_COLS + cc];
+            for (int g = 0; g < DC_GROUPS; ++g) sum += red[g * DC_RED_STRIDE + t * DC_COLS + cc];
             for (int s = 0; s <= t; ++s) sum = fmaf(pt[t * DC_CHUNK + s], vt[s * DC_COLS + cc], sum);
             if (tile * DC_COLS + cc < dv) o[(size_t)(first + t) * n_heads * dv + (size_t)h * dv + tile * DC_COLS + cc] = sum;
         }
@@ -337,14 +350,14 @@ template <int RH>
 static int decay_chunk_scan_launch(dim3 grid, cudaStream_t stream, const float* qd, const float* kd, const float* ed,
                                    const float* P, const float* v, int ldv, int act, float* state, const int* slots,
                                    const int* cu, float* o, int n_heads, int dk, int dv) {
-    const size_t smem = sizeof(float) * ((size_t)2 * DC_CHUNK * 16 * RH + DC_CHUNK * DC_COLS + DC_CHUNK * DC_CHUNK + 16 * RH +
-                                         16 * DC_CHUNK * DC_COLS);
+    const size_t smem = sizeof(float) * ((size_t)2 * DC_CHUNK * DC_GROUPS * RH + DC_CHUNK * DC_COLS + DC_CHUNK * DC_CHUNK +
+                                         DC_GROUPS * RH + DC_GROUPS * DC_RED_STRIDE);
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(decay_chunk_scan_kernel<RH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attr_set = true;
     }
-    mv_launch(decay_chunk_scan_kernel<RH>, grid, DC_THREADS, smem, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o,
+    mv_launch(decay_chunk_scan_kernel<RH>, grid, DC_SCAN_THREADS, smem, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o,
               n_heads, dk, dv);
     return mv_launch_status();
 }
@@ -371,7 +384,6 @@ MV_API int mv_decay_scan_chunked(const float* q, int ldq, const float* k, int ld
     int code = mv_launch_status();
     if (code) return code;
     const dim3 grid((dv + DC_COLS - 1) / DC_COLS, n_heads, n_seqs);
-    if (dk <= 64) return decay_chunk_scan_launch<4>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
-    if (dk <= 128) return decay_chunk_scan_launch<8>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
-    return decay_chunk_scan_launch<16>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    if (dk <= 128) return decay_chunk_scan_launch<4>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
+    return decay_chunk_scan_launch<8>(grid, stream, qd, kd, ed, P, v, ldv, act, state, slots, cu, o, n_heads, dk, dv);
 }
