@@ -139,6 +139,50 @@ MV_API int mv_rmsnorm_add(const float* y, const float* w, float* resid, int N, i
     return mv_launch_status();
 }
 
+// ------------------------- the same, followed by the layer norm of the row it has just completed
+// resid[n, :] += y / rms(y) * w, then out[n, :] = layer_norm(resid[n, :]) * ln_w: the last kernel of a layer and the
+// first of the next in one, for layers that end with a normed input added to the residual stream.  A thread reads
+// back only elements that it wrote itself.
+template <typename TO>
+__global__ void rmsnorm_add_layernorm_kernel(const float* __restrict__ y, const float* __restrict__ w, float eps,
+                                             float* __restrict__ resid, const float* __restrict__ ln_w, float ln_eps,
+                                             TO* __restrict__ out, int H) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const float* yr = y + (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) ss = fmaf(yr[h], yr[h], ss);
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+    float* rr = resid + (size_t)blockIdx.x * H;
+    float sum = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = rr[h] + yr[h] * scale * w[h];
+        rr[h] = v;
+        sum += v;
+    }
+    const float mean = mv_block_sum(sum, scratch) / (float)H;
+    float dev = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float d = rr[h] - mean;
+        dev = fmaf(d, d, dev);
+    }
+    const float rstd = 1.0f / sqrtf(mv_block_sum(dev, scratch) / (float)H + ln_eps);
+    TO* orow = out + (size_t)blockIdx.x * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) orow[h] = mv_from_f32<TO>((rr[h] - mean) * rstd * ln_w[h]);
+}
+
+MV_API int mv_rmsnorm_add_layernorm(const float* y, const float* w, float eps, float* resid, const float* ln_w,
+                                    float ln_eps, void* out, int out_dtype, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == MV_DT_BF16)
+        mv_launch(rmsnorm_add_layernorm_kernel<__nv_bfloat16>, N, threads, 0, stream, y, w, eps, resid, ln_w, ln_eps,
+                  (__nv_bfloat16*)out, H);
+    else
+        mv_launch(rmsnorm_add_layernorm_kernel<float>, N, threads, 0, stream, y, w, eps, resid, ln_w, ln_eps, (float*)out, H);
+    return mv_launch_status();
+}
+
 // ------------------------------------------------------ clamped gated activation
 // h[n, f] = g * sigmoid(alpha * g) * (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit);
 // gate = gu[n, f], up = gu[n, F + f].

@@ -48,6 +48,7 @@ _SIGNATURES = {
         "mv_layernorm": [_P, _P, _P, _I, _P, _I, _I, _F, _P],
         "mv_gated_rmsnorm": [_P, _P, _I, _P, _I, _P, _I, _I, _I, _I, _F, _I, _P],
         "mv_rmsnorm_add": [_P, _P, _P, _I, _I, _F, _P],
+        "mv_rmsnorm_add_layernorm": [_P, _P, _F, _P, _P, _F, _P, _I, _I, _I, _P],
         "mv_glu_clamped": [_P, _P, _I, _I, _I, _F, _F, _P],
         "mv_table_gate": [_P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
         "mv_table_gate_proj": [_P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
@@ -394,6 +395,19 @@ def rmsnorm_add(y: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.Tenso
         _need(resid, "residual stream", torch.float32, (N, H)), N, H, float(eps), _stream()), "mv_rmsnorm_add")
     account(N * H * 12)
     return resid
+
+
+def rmsnorm_add_layernorm(y: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.Tensor, ln_w: torch.Tensor,
+                          ln_eps: float, out: torch.Tensor) -> torch.Tensor:
+    """``rmsnorm_add`` followed by ``layernorm`` of the rows it has completed, in one kernel: resid += y / rms(y) * w,
+    out = layer_norm(resid) * ln_w (no bias)."""
+    N, H = y.shape
+    _check(_fn("core", "mv_rmsnorm_add_layernorm")(
+        _need(y, "rmsnorm_add y", torch.float32), _need(w, "rmsnorm_add weight", torch.float32, (H,)), float(eps),
+        _need(resid, "residual stream", torch.float32, (N, H)), _need(ln_w, "layernorm weight", torch.float32, (H,)),
+        float(ln_eps), _need(out, "layernorm out", None, (N, H)), _dt(out), N, H, _stream()), "mv_rmsnorm_add_layernorm")
+    account(N * H * (12 + out.element_size()))
+    return out
 
 
 def glu_clamped(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:

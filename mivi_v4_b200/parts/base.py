@@ -10,7 +10,8 @@ mixer         cache_need() -> KVNeed | StateNeed | None | a list of those
               forward(u[N, hidden], resid, step, cache_view) -> None   (a list of views for a list of needs)
 feed_forward  forward(g[N, hidden], resid, step) -> None; one that overrides cache_need() is also passed
               view=<its view or list of views>
-token_input   forward(resid, step) -> None: a per-layer input that depends on the token ids
+token_input   forward(resid, step) -> None: a per-layer input that depends on the token ids; one with
+              ``takes_norm = True`` also takes then_norm=(layer norm part, out) and runs that norm on its result
 block         cache_need(); forward(resid, step, cache_view) -> None
 embedding     forward(step) -> resid f32[N, hidden]
 head          forward(f[n, hidden], step, embedding) -> logits f32[n, vocab]

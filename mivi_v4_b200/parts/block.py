@@ -3,6 +3,7 @@ from __future__ import annotations
 
 from ..ops.kernels import profile_stage
 from .base import Part
+from .norm import LayerNorm
 from .registry import register
 
 
@@ -105,11 +106,23 @@ class PreNormOptionalBlock(Part):
     def cache_need(self):
         return self.mixer.cache_need()
 
-    def forward(self, resid, step, view) -> None:
+    def entry_link(self, step):
+        """No product carries this block's norms; the method is there so that the model tells ``forward`` which
+        block runs next (``after``)."""
+        return None
+
+    def forward(self, resid, step, view, after=None) -> None:
+        """``after``: the block that runs next in this step, if any.  Where this block ends with a token input and
+        the next one is of this kind with a layer norm first, that norm runs inside the token input's last kernel
+        and its rows are handed over through the step (``step.handed``)."""
         N, H = resid.shape
-        u = self.scratch(step, "normed", (N, H), step.dtype)
-        with profile_stage("norm"):
-            self.mixer_norm.forward(resid, u)
+        handed, step.handed = getattr(step, "handed", None), None
+        if handed is not None and handed[0] is self.mixer_norm:
+            u = handed[1]
+        else:
+            u = self.scratch(step, "normed", (N, H), step.dtype)
+            with profile_stage("norm"):
+                self.mixer_norm.forward(resid, u)
         with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
             self.mixer.forward(u, resid, step, view)
         if self.ffn is not None:
@@ -119,5 +132,14 @@ class PreNormOptionalBlock(Part):
             with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
                 self.ffn.forward(g, resid, step)
         if self.token_input is not None:
+            nxt = after.mixer_norm if isinstance(after, PreNormOptionalBlock) and isinstance(after.mixer_norm, LayerNorm) \
+                and getattr(self.token_input, "takes_norm", False) else None
             with profile_stage("token_input " + getattr(self.token_input, "kind", "?")):
-                self.token_input.forward(resid, step)
+                if nxt is not None:
+                    # another buffer than "normed": this block's rows there are done with, the next block's
+                    # second norm will write there while its first norm's rows are still read
+                    out = self.scratch(step, "normed_entry", (N, H), step.dtype)
+                    self.token_input.forward(resid, step, then_norm=(nxt, out))
+                    step.handed = (nxt, out)
+                else:
+                    self.token_input.forward(resid, step)

@@ -20,6 +20,8 @@ class GatedTableInput(Part):
     the norm a root-mean-square norm with a plain weight.  The residual stream is rounded to the model's
     dtype for the product with G; gelu, the norm and the sum are float32."""
 
+    takes_norm = True            # forward(..., then_norm=...) runs the layer norm that follows inside its last kernel
+
     def __init__(self, hidden: int, vocab: int, dim: int, index: int, table_width: int, eps: float):
         self.hidden, self.vocab, self.dim = int(hidden), int(vocab), int(dim)
         self.index, self.table_width, self.eps = int(index), int(table_width), float(eps)
@@ -35,7 +37,9 @@ class GatedTableInput(Part):
     def load(self, t) -> None:
         self.table, self.w_gate, self.w_proj, self.norm = t["table"], t["gate"], t["proj"], t["norm"]
 
-    def forward(self, resid, step) -> None:
+    def forward(self, resid, step, then_norm=None) -> None:
+        """``then_norm``: (layer norm part, out) of the norm that follows at once on the finished rows (the next
+        layer's first one): it then runs inside this part's last kernel and ``out`` holds its result."""
         N, H = resid.shape
         g = self.scratch(step, "g", (N, self.dim), step.dtype)
         if K.table_gate_proj_ok(N, self.w_gate, self.table, step.dtype):
@@ -50,4 +54,7 @@ class GatedTableInput(Part):
             K.table_gate(p, self.table, self.index * self.dim, step.tokens, g)
         y = self.scratch(step, "y", (N, H), torch.float32)
         linear(g, self.w_proj, y)
-        K.rmsnorm_add(y, self.norm, self.eps, resid)
+        if then_norm is not None:
+            K.rmsnorm_add_layernorm(y, self.norm, self.eps, resid, then_norm[0].weight, then_norm[0].eps, then_norm[1])
+        else:
+            K.rmsnorm_add(y, self.norm, self.eps, resid)

@@ -60,6 +60,14 @@ def test_rmsnorm_add_glu_table_gate_round():
     want = resid.double().cpu() + P.rms_unit(y.double().cpu(), 1e-5) * w.double().cpu()
     K.rmsnorm_add(y, w, 1e-5, resid)
     close(resid, want, torch.float32)
+    for dt in (torch.float32, torch.bfloat16):                # the same with the next layer norm in the same kernel
+        resid2 = torch.randn(N, H).to(DEV) * 2 + 3
+        ln_w = torch.randn(H).to(DEV)
+        new = resid2.double().cpu() + P.rms_unit(y.double().cpu(), 1e-5) * w.double().cpu()
+        out = torch.full((N, H), float("nan"), dtype=dt, device=DEV)
+        K.rmsnorm_add_layernorm(y, w, 1e-5, resid2, ln_w, 1e-4, out)
+        close(resid2, new, torch.float32)
+        close(out, P.layer_norm(new, ln_w.double().cpu(), 1e-4), dt)
     gu = (torch.randn(N, 2 * 33) * 3).to(DEV)
     for dt in (torch.float32, torch.bfloat16):
         out = torch.empty((N, 33), dtype=dt, device=DEV)
