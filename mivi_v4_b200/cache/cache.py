@@ -130,7 +130,8 @@ class SequenceCache:
         self.kv_groups: List[int] = [i for i, g in enumerate(plan.groups) if isinstance(g.need, KVNeed)]
         self.state_groups: List[int] = [i for i, g in enumerate(plan.groups) if isinstance(g.need, StateNeed)]
         self.pages: Dict[int, IndexPool] = {g: IndexPool(n_pages, "page") for g in self.kv_groups}
-        self.windowed: List[int] = [g for g in self.kv_groups if plan.groups[g].need.window > 0]
+        self.windowed: List[int] = [g for g in self.kv_groups
+                                    if plan.groups[g].need.window > 0 or plan.groups[g].need.chunk > 0]
         # the same bookkeeping as arrays over all slots: length, assigned or not, blocks that have a page
         # entry, and per KV group the page of each block (0 where there is none)
         self._len = np.zeros(max(n_slots, 1), dtype=np.int64)
@@ -257,8 +258,11 @@ class SequenceCache:
         length = int(self._len[slot])
         for gi in self.windowed:
             need = self.plan.groups[gi].need
-            first_needed = max(0, length - need.window + 1)     # the next token reads keys from here on
-            kept = -(-need.keep_first // self.page_size)        # blocks that hold one of the kept first tokens
+            if need.chunk > 0:                                  # the next token reads its own chunk's keys only
+                first_needed, kept = length - length % need.chunk, 0
+            else:
+                first_needed = max(0, length - need.window + 1)     # the next token reads keys from here on
+                kept = -(-need.keep_first // self.page_size)        # blocks that hold one of the kept first tokens
             for blk in range(kept, min(first_needed // self.page_size, len(seq.pages[gi]))):
                 if seq.pages[gi][blk] is not None:
                     self.pages[gi].give(seq.pages[gi][blk])

@@ -16,12 +16,15 @@ class KVNeed:
     are given back while the sequence is still running; ``keep_first`` tokens at the start of the sequence
     stay readable for good, so the pages that hold any of them are never given back.  ``v_dim`` > 0: values
     of another size than the keys' ``head_dim``; a page is then one flat row, the keys [kv head][row][head_dim]
-    followed by the values [kv head][row][v_dim]."""
+    followed by the values [kv head][row][v_dim].  ``chunk`` > 0 (instead of a window): a token reads only the
+    keys of its own chunk of ``chunk`` positions, counted from the sequence's start, so the pages that lie wholly
+    before the chunk of the next token are given back."""
     n_kv_heads: int
     head_dim: int
     window: int = 0
     v_dim: int = 0
     keep_first: int = 0
+    chunk: int = 0
 
     @property
     def value_dim(self) -> int:

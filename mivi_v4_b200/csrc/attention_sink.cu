@@ -9,7 +9,12 @@
 //     j < keep_first;
 //   * a sink: a learned number per head whose exponential joins the softmax's denominator, with no
 //     value of its own;
-//   * a gate per token and head, sigmoid of a logit, on the head's output.
+//   * a gate per token and head, sigmoid of a logit, on the head's output;
+//   * the q and k norm per head instead (one weight of the head's size, shared by all heads);
+//   * a factor on the rotation's cos and sin (a rotation whose stretched frequencies are made up for
+//     by longer vectors);
+//   * a chunked mask: query i reads key j <= i only if both lie in the same chunk of `chunk` positions,
+//     counted from the sequence's position 0.
 // Each is a parameter (0 or null turns it off).
 //
 // Cache layout of one layer's page: [kv head][row][dk] keys, then [kv head][row][dv] values; with
@@ -28,8 +33,10 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
                         const float* __restrict__ wk, float eps, int rot_dims, const float* __restrict__ inv_freq,
                         const int* __restrict__ positions, const int* __restrict__ seq_of,
                         const int* __restrict__ page_table, int table_stride, int page_shift, T* __restrict__ pool,
-                        long long page_stride, T* __restrict__ q_out, int nh, int nkv, int dk, int dv) {
+                        long long page_stride, T* __restrict__ q_out, int nh, int nkv, int dk, int dv, int per_head,
+                        float amplitude) {
     mv_pdl_begin();
+    extern __shared__ float head_scale[];           // [nh + nkv] with per_head
     __shared__ float scratch[33];
     __shared__ float rot_sn[AS_MAX_DIM / 2], rot_cs[AS_MAX_DIM / 2];
     const int n = blockIdx.x;
@@ -37,15 +44,35 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
     const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv;
     // the rotation of pair i at this token's position is the same for every head: worked out once
     for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x)
-        sincosf((float)positions[n] * inv_freq[i], &rot_sn[i], &rot_cs[i]);
+    {
+        float sn, cs;
+        sincosf((float)positions[n] * inv_freq[i], &sn, &cs);
+        rot_sn[i] = sn * amplitude;
+        rot_cs[i] = cs * amplitude;
+    }
     const float* qr = row;
     const float* kr = row + nq;
     const float* vr = kr + nk;
     float sq = 0.f, sk = 0.f;
-    for (int e = threadIdx.x; e < nq; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
-    for (int e = threadIdx.x; e < nk; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
-    const float q_scale = wq ? 1.0f / sqrtf(mv_block_sum(sq, scratch) / (float)nq + eps) : 1.f;
-    const float k_scale = wk ? 1.0f / sqrtf(mv_block_sum(sk, scratch) / (float)nk + eps) : 1.f;
+    float q_scale = 1.f, k_scale = 1.f;
+    if (per_head) {
+        // a warp a head: q's heads, then k's (they follow q in the row)
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int hh = warp; hh < nh + nkv; hh += (blockDim.x >> 5)) {
+            const float* hr = row + (size_t)hh * dk;
+            float ss = 0.f;
+            for (int d = lane; d < dk; d += 32) ss = fmaf(hr[d], hr[d], ss);
+            ss = mv_warp_sum(ss);
+            if (lane == 0) head_scale[hh] = 1.0f / sqrtf(ss / (float)dk + eps);
+        }
+        __syncthreads();
+    } else {
+        for (int e = threadIdx.x; e < nq; e += blockDim.x) sq = fmaf(qr[e], qr[e], sq);
+        for (int e = threadIdx.x; e < nk; e += blockDim.x) sk = fmaf(kr[e], kr[e], sk);
+        q_scale = wq ? 1.0f / sqrtf(mv_block_sum(sq, scratch) / (float)nq + eps) : 1.f;
+        k_scale = wk ? 1.0f / sqrtf(mv_block_sum(sk, scratch) / (float)nk + eps) : 1.f;
+    }
+    __syncthreads();                                 // the rotation's table is complete whatever norm ran
     const int pos = positions[n];
     const int page_size = 1 << page_shift;
     const int page = page_table[(size_t)seq_of[n] * table_stride + (pos >> page_shift)];
@@ -61,14 +88,15 @@ qkv_prepare_wide_kernel(const float* __restrict__ proj, int ld, const float* __r
         const int f = is_q ? e : e - nq;
         const float* src = is_q ? qr : kr;
         const float* w = is_q ? wq : wk;
-        const float sc = is_q ? q_scale : k_scale;
         const int head = f / dk, d = f - head * dk;
-        float a = src[f] * sc * (w ? w[f] : 1.f);
+        const float sc = per_head ? (w ? head_scale[is_q ? head : nh + head] : 1.f) : (is_q ? q_scale : k_scale);
+        const int wo = per_head ? head * dk : 0;           // a per-head weight is indexed inside the head
+        float a = src[f] * sc * (w ? w[f - wo] : 1.f);
         if (d < rot_dims) {
             // element d < half pairs with d + half: (u, v) -> (u cos - v sin, v cos + u sin)
             const int i = d < half ? d : d - half;
             const int fp = d < half ? f + half : f - half;
-            const float b = src[fp] * sc * (w ? w[fp] : 1.f);
+            const float b = src[fp] * sc * (w ? w[fp - wo] : 1.f);
             const float sn = rot_sn[i], cs = rot_cs[i];
             a = d < half ? a * cs - b * sn : a * cs + b * sn;
         }
@@ -89,9 +117,11 @@ MV_GUARD_SETTER(attention_sink)
 MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const float* wk, float eps, int rot_dims,
                                const float* inv_freq, const int* positions, const int* seq_of, const int* page_table,
                                int table_stride, int page_size, void* pool, long long page_stride, void* q_out,
-                               int dtype, int N, int nh, int nkv, int dk, int dv, cudaStream_t stream) {
+                               int dtype, int N, int nh, int nkv, int dk, int dv, int per_head, float amplitude,
+                               cudaStream_t stream) {
     if (N <= 0) return 0;
-    if ((page_size & (page_size - 1)) || rot_dims % 2 || rot_dims > dk || (rot_dims && !inv_freq))
+    const size_t smem = per_head ? sizeof(float) * (size_t)(nh + nkv) : 0;
+    if ((page_size & (page_size - 1)) || rot_dims % 2 || rot_dims > dk || (rot_dims && !inv_freq) || smem > 32768)
         return (int)cudaErrorInvalidValue;
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
@@ -99,13 +129,13 @@ MV_API int mv_qkv_prepare_wide(const float* proj, int ld, const float* wq, const
     const int parts = N >= 256 ? 1 : (N >= 64 ? 2 : 6);
     const dim3 grid(N, parts);
     if (dtype == MV_DT_BF16)
-        mv_launch(qkv_prepare_wide_kernel<__nv_bfloat16>, grid, 256, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+        mv_launch(qkv_prepare_wide_kernel<__nv_bfloat16>, grid, 256, smem, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
                   positions, seq_of, page_table, table_stride, page_shift, (__nv_bfloat16*)pool, page_stride,
-                  (__nv_bfloat16*)q_out, nh, nkv, dk, dv);
+                  (__nv_bfloat16*)q_out, nh, nkv, dk, dv, per_head, amplitude);
     else
-        mv_launch(qkv_prepare_wide_kernel<float>, grid, 256, 0, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
+        mv_launch(qkv_prepare_wide_kernel<float>, grid, 256, smem, stream, proj, ld, wq, wk, eps, rot_dims, inv_freq,
                   positions, seq_of, page_table, table_stride, page_shift, (float*)pool, page_stride, (float*)q_out, nh,
-                  nkv, dk, dv);
+                  nkv, dk, dv, per_head, amplitude);
     return mv_launch_status();
 }
 
@@ -127,7 +157,7 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
                       const int* __restrict__ positions, const int* __restrict__ seq_of,
                       const float* __restrict__ sinks, const float* __restrict__ gate, int ld_gate,
                       T* __restrict__ o, int N, int nh, int nkv, int dk, int dv, float scale, float cap, int window,
-                      int keep_first) {
+                      int keep_first, int chunk) {
     mv_pdl_begin();
     extern __shared__ __align__(16) float as_smem[];
     float* qs = as_smem;                            // [GT][dk]
@@ -159,8 +189,9 @@ attention_sink_kernel(const T* __restrict__ q, const T* __restrict__ pool, long 
         m[i] = first ? sinks[h0 + i] : -INFINITY;
         l[i] = first ? 1.f : 0.f;
     }
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const int keep = min(keep_first, lo);
+    // a chunked mask: the keys from the start of the query's own chunk on
+    const int lo = chunk > 0 ? pos - pos % chunk : (window > 0 ? max(0, pos - window + 1) : 0);
+    const int keep = chunk > 0 ? 0 : min(keep_first, lo);
     const int total = keep + (pos - lo + 1);
     const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
@@ -291,7 +322,7 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
                              int table_stride, int page_size, const int* positions, const int* seq_of,
                              const float* sinks, const float* gate, int ld_gate, void* o, int dtype, int N, int nh,
                              int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-                             int head_tile, cudaStream_t stream) {
+                             int head_tile, int chunk, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (dk < 1 || dk > AS_MAX_DIM || dv < 1 || dv > AS_MAX_DIM || nkv < 1 || nh % nkv || (page_size & (page_size - 1)))
         return (int)cudaErrorInvalidValue;
@@ -311,7 +342,7 @@ MV_API int mv_attention_sink(const void* q, const void* pool, long long page_str
 #define AS_LAUNCH(T, V, GTV)                                                                                         \
     mv_launch(attention_sink_kernel<T, V, GTV>, blocks, AS_WARPS * 32, smem, stream, (const T*)q, (const T*)pool,    \
               page_stride, page_table, table_stride, page_shift, positions, seq_of, sinks, gate, ld_gate, (T*)o, N,  \
-              nh, nkv, dk, dv, scale, cap, window, keep_first)
+              nh, nkv, dk, dv, scale, cap, window, keep_first, chunk)
 #define AS_PICK(T, V)                                                                                                \
     do {                                                                                                             \
         if (gt == 4) AS_LAUNCH(T, V, 4); else if (gt == 2) AS_LAUNCH(T, V, 2); else AS_LAUNCH(T, V, 1);             \

@@ -6,7 +6,8 @@
 // (mma.sync m16n8k16, float32 accumulation) with the running-maximum softmax in float32 registers between
 // them.  What differs: the key blocks a tile walks are the blocks of the kept first tokens followed by the
 // blocks of its window; the scores are scaled and capped in float32 before the maximum is taken; the sink
-// starts every row's maximum and denominator; the output is multiplied by the sigmoid of the row's gate.
+// starts every row's maximum and denominator; the output is multiplied by the sigmoid of the row's gate;
+// with a chunked mask the walk starts at the first query's chunk and keys before a row's own chunk are masked.
 // Key and value sizes are run-time multiples of 16 up to the template's bounds.
 #include "common.cuh"
 
@@ -49,7 +50,7 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
                               int page_shift, const int* __restrict__ cu, const int* __restrict__ starts,
                               const float* __restrict__ sinks, const float* __restrict__ gate, int ld_gate,
                               __nv_bfloat16* __restrict__ o, int B, int nh, int nkv, int dk, int dv, float scale,
-                              float cap, int window, int keep_first) {
+                              float cap, int window, int keep_first, int chunk) {
     const int ldk = dk + 8, ldv = dv + 8;             // padded rows: conflict-free fragment loads
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [2][KB][ldk]
@@ -75,6 +76,7 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
 
     const int qi0 = warp * 16 + gq, qi1 = qi0 + 8;
     const int p0 = pos0 + qi0, p1 = pos0 + qi1;
+    const int cs0 = chunk > 0 ? p0 - p0 % chunk : 0, cs1 = chunk > 0 ? p1 - p1 % chunk : 0;    // where the rows' chunks start
     unsigned qf[DKM / 16][4];
     {
         const __nv_bfloat16* r0 = q + ((size_t)(row0 + min(qi0, nq - 1)) * nh + h) * dk;
@@ -104,9 +106,11 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
     // key blocks this tile walks: the blocks that hold kept first tokens and lie before the window's
     // blocks, then from the first query's window start to the last query's position
     const int last_pos = pos0 + nq - 1;
-    const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+    // with a chunked mask (chunk > 0: a query reads only the keys of its own chunk of positions) the first
+    // query's chunk starts the walk
+    const int first_key = chunk > 0 ? pos0 - pos0 % chunk : (window > 0 ? max(0, pos0 - window + 1) : 0);
     const int kb_begin = first_key / KB, kb_end = last_pos / KB + 1;
-    const int n_kept = (window > 0 && keep_first > 0) ? min((keep_first + KB - 1) / KB, kb_begin) : 0;
+    const int n_kept = (chunk == 0 && window > 0 && keep_first > 0) ? min((keep_first + KB - 1) / KB, kb_begin) : 0;
     const int n_iter = n_kept + kb_end - kb_begin;
 
     auto load_block = [&](int kb, int buf) {
@@ -154,7 +158,7 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
         // scale and cap, mask, then the running maximum of the two rows
         const int key0 = kb * KB;
         const bool need_mask = it < n_kept || key0 + KB - 1 > pos0 + warp * 16 ||
-                               (window > 0 && key0 <= pos0 + warp * 16 + 15 - window);
+                               (chunk > 0 ? key0 < cs1 : (window > 0 && key0 <= pos0 + warp * 16 + 15 - window));
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int j = 0; j < KB / 8; ++j) {
@@ -170,7 +174,8 @@ attention_sink_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bf
                 if (need_mask) {
                     const int t = key0 + j * 8 + 2 * t4 + (e & 1);
                     const int p = (e < 2) ? p0 : p1;
-                    if (t > p || (window > 0 && t <= p - window && t >= keep_first)) sc = -INFINITY;
+                    if (t > p || (chunk > 0 ? t < ((e < 2) ? cs0 : cs1)
+                                            : (window > 0 && t <= p - window && t >= keep_first))) sc = -INFINITY;
                 }
                 s[j][e] = sc;
             }
@@ -250,7 +255,7 @@ template <int DKM, int DVM>
 int launch(const void* q, const void* pool, long long page_stride, const int* page_table, int table_stride,
            int page_shift, const int* cu, const int* starts, const float* sinks, const float* gate, int ld_gate, void* o,
            int N, int B, int nh, int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-           cudaStream_t stream) {
+           int chunk, cudaStream_t stream) {
     const size_t smem = (size_t)2 * KB * (dk + 8 + dv + 8) * sizeof(__nv_bfloat16);
     static bool attr_set = false;
     if (!attr_set) {
@@ -261,7 +266,7 @@ int launch(const void* q, const void* pool, long long page_stride, const int* pa
     dim3 grid((N + QT - 1) / QT + B, nh);         // an upper bound of the tiles; spare blocks return at once
     attention_sink_prefill_kernel<DKM, DVM><<<grid, NWARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, page_stride, page_table, table_stride, page_shift, cu,
-        starts, sinks, gate, ld_gate, (__nv_bfloat16*)o, B, nh, nkv, dk, dv, scale, cap, window, keep_first);
+        starts, sinks, gate, ld_gate, (__nv_bfloat16*)o, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk);
     return mv_launch_status();
 }
 
@@ -275,7 +280,7 @@ MV_API int mv_attention_sink_prefill(const void* q, const void* pool, long long 
                                      int table_stride, int page_size, const int* cu, const int* starts,
                                      const float* sinks, const float* gate, int ld_gate, void* o, int N, int B, int nh,
                                      int nkv, int dk, int dv, float scale, float cap, int window, int keep_first,
-                                     cudaStream_t stream) {
+                                     int chunk, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (nkv < 1 || nh % nkv || (page_size & (page_size - 1)) || dk % 16 || dv % 16 || dk < 16 || dv < 16 || dk > 128 ||
         dv > 128)
@@ -284,7 +289,7 @@ MV_API int mv_attention_sink_prefill(const void* q, const void* pool, long long 
     while ((1 << page_shift) < page_size) ++page_shift;
 #define AS_GO(A, C)                                                                                                  \
     return launch<A, C>(q, pool, page_stride, page_table, table_stride, page_shift, cu, starts, sinks, gate, ld_gate, o, \
-                        N, B, nh, nkv, dk, dv, scale, cap, window, keep_first, stream)
+                        N, B, nh, nkv, dk, dv, scale, cap, window, keep_first, chunk, stream)
     if (dk <= 64 && dv <= 64) AS_GO(64, 64);
     if (dk <= 64) AS_GO(64, 128);
     if (dv <= 64) AS_GO(128, 64);

@@ -28,6 +28,54 @@ MV_API int mv_embed(const void* table, int table_dtype, const int* tok, float* x
     return mv_launch_status();
 }
 
+// x = table[token] * scale + pos_table[position]: a scaled token embedding plus a learned position vector;
+// ``rounded`` (or null) also gets the row in the model's dtype, for a first layer that reads the stream itself.
+template <typename T, typename TO>
+__global__ void embed_scaled_pos_kernel(const T* __restrict__ table, const int* __restrict__ tok, float scale,
+                                        const T* __restrict__ pos_table, const int* __restrict__ positions,
+                                        float* __restrict__ x, TO* __restrict__ rounded, int H) {
+    mv_pdl_begin();
+    const int n = blockIdx.x;
+    const T* row = table + (size_t)tok[n] * H;
+    const T* prow = pos_table ? pos_table + (size_t)positions[n] * H : nullptr;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = fmaf(mv_to_f32(row[h]), scale, prow ? mv_to_f32(prow[h]) : 0.f);
+        x[(size_t)n * H + h] = v;
+        if (rounded) rounded[(size_t)n * H + h] = mv_from_f32<TO>(v);
+    }
+}
+
+MV_API int mv_embed_scaled_pos(const void* table, int table_dtype, const int* tok, float scale, const void* pos_table,
+                               const int* positions, float* x, void* rounded, int rounded_dtype, int N, int H,
+                               cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 1024 ? 256 : 128;
+#define EP_LAUNCH(T, TO)                                                                                          \
+    mv_launch(embed_scaled_pos_kernel<T, TO>, N, threads, 0, stream, (const T*)table, tok, scale, (const T*)pos_table, \
+              positions, x, (TO*)rounded, H)
+    if (table_dtype == MV_DT_BF16) {
+        if (rounded && rounded_dtype == MV_DT_F32) EP_LAUNCH(__nv_bfloat16, float); else EP_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    } else {
+        if (rounded && rounded_dtype == MV_DT_BF16) EP_LAUNCH(float, __nv_bfloat16); else EP_LAUNCH(float, float);
+    }
+#undef EP_LAUNCH
+    return mv_launch_status();
+}
+
+// x <- cap * tanh(x / cap), in place (logits that are capped smoothly)
+__global__ void softcap_kernel(float* __restrict__ x, long long total, float cap, float inv_cap) {
+    mv_pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+MV_API int mv_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (!(cap > 0.f)) return (int)cudaErrorInvalidValue;
+    mv_launch(softcap_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, x, total, cap, 1.0f / cap);
+    return mv_launch_status();
+}
+
 // The same, and the first norm of the first layer handed to the product that follows (steps of few
 // tokens): xg = bf16(x * g), and per warp the sum of its elements' squares, one partial sum a warp;
 // the product multiplies its results by rsqrt(sum of the partials / H + eps).

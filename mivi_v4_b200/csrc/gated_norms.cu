@@ -44,6 +44,9 @@ MV_API int mv_layernorm(const float* x, const float* w, void* y, int y_dtype, co
 // A row of C values is cut into groups of ``group``; each group is divided by its root mean
 // square (eps inside the root), multiplied by w[c mod w_len] and by act(gate[n, c]) with act =
 // silu (0) or sigmoid (1).  One warp per (row, group).  The gate has its own row stride.
+// act = 2: the gate comes BEFORE the norm: the values x * silu(gate) are divided by THEIR root mean
+// square and multiplied by w.
+__device__ __forceinline__ float gn_gated_first(float x, float g) { return x * (g / (1.0f + expf(-g))); }
 template <typename TO>
 __global__ void __launch_bounds__(256)
 gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gate, int ld_gate,
@@ -57,16 +60,21 @@ gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gate
     const long long n = wid / per_row;
     const int c0 = (int)(wid - n * per_row) * group;
     const float* xr = x + (size_t)n * C + c0;
+    const float* gr = gate + (size_t)n * ld_gate + c0;
     float ss = 0.f;
-    for (int d = lane; d < group; d += 32) ss = fmaf(xr[d], xr[d], ss);
+    if (act == 2)
+        for (int d = lane; d < group; d += 32) { const float v = gn_gated_first(xr[d], gr[d]); ss = fmaf(v, v, ss); }
+    else
+        for (int d = lane; d < group; d += 32) ss = fmaf(xr[d], xr[d], ss);
     ss = mv_warp_sum(ss);
     const float scale = 1.0f / sqrtf(ss / (float)group + eps);
-    const float* gr = gate + (size_t)n * ld_gate + c0;
     TO* yr = y + (size_t)n * C + c0;
     for (int d = lane; d < group; d += 32) {
         const float g = gr[d];
         const float sg = 1.0f / (1.0f + expf(-g));
-        yr[d] = mv_from_f32<TO>(xr[d] * scale * w[(c0 + d) % w_len] * (act == 0 ? g * sg : sg));
+        const float wv = w[(c0 + d) % w_len];
+        yr[d] = mv_from_f32<TO>(act == 2 ? gn_gated_first(xr[d], g) * scale * wv
+                                         : xr[d] * scale * wv * (act == 0 ? g * sg : sg));
     }
 }
 
@@ -82,15 +90,20 @@ gated_rmsnorm_block_kernel(const float* __restrict__ x, const float* __restrict_
     const long long n = blockIdx.x / per_row;
     const int c0 = (int)(blockIdx.x - n * per_row) * group;
     const float* xr = x + (size_t)n * C + c0;
-    float ss = 0.f;
-    for (int d = threadIdx.x; d < group; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
-    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)group + eps);
     const float* gr = gate + (size_t)n * ld_gate + c0;
+    float ss = 0.f;
+    if (act == 2)
+        for (int d = threadIdx.x; d < group; d += blockDim.x) { const float v = gn_gated_first(xr[d], gr[d]); ss = fmaf(v, v, ss); }
+    else
+        for (int d = threadIdx.x; d < group; d += blockDim.x) ss = fmaf(xr[d], xr[d], ss);
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)group + eps);
     TO* yr = y + (size_t)n * C + c0;
     for (int d = threadIdx.x; d < group; d += blockDim.x) {
         const float g = gr[d];
         const float sg = 1.0f / (1.0f + expf(-g));
-        yr[d] = mv_from_f32<TO>(xr[d] * scale * w[(c0 + d) % w_len] * (act == 0 ? g * sg : sg));
+        const float wv = w[(c0 + d) % w_len];
+        yr[d] = mv_from_f32<TO>(act == 2 ? gn_gated_first(xr[d], g) * scale * wv
+                                         : xr[d] * scale * wv * (act == 0 ? g * sg : sg));
     }
 }
 
@@ -136,6 +149,42 @@ MV_API int mv_rmsnorm_add(const float* y, const float* w, float* resid, int N, i
     if (N <= 0) return 0;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     mv_launch(rmsnorm_add_kernel, N, threads, 0, stream, y, w, resid, H, eps);
+    return mv_launch_status();
+}
+
+// The same for a sublayer whose norm sits on its OUTPUT (x += norm(f(x))), where the output may be the
+// weighted sum of two branches, y = s1 y1 + s2 y2 (y2 null: y = s1 y1), and where the next sublayer reads
+// the completed row rounded to the model's dtype (rounded null: not written).
+template <typename TO>
+__global__ void rmsnorm_add_sum_kernel(const float* __restrict__ y1, float s1, const float* __restrict__ y2, float s2,
+                                       const float* __restrict__ w, float* __restrict__ resid, TO* __restrict__ rounded,
+                                       int H, float eps) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * H;
+    float ss = 0.f;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = y2 ? fmaf(s2, y2[base + h], s1 * y1[base + h]) : s1 * y1[base + h];
+        ss = fmaf(v, v, ss);
+    }
+    const float scale = 1.0f / sqrtf(mv_block_sum(ss, scratch) / (float)H + eps);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float v = y2 ? fmaf(s2, y2[base + h], s1 * y1[base + h]) : s1 * y1[base + h];
+        const float r = resid[base + h] + v * scale * w[h];
+        resid[base + h] = r;
+        if (rounded) rounded[base + h] = mv_from_f32<TO>(r);
+    }
+}
+
+MV_API int mv_rmsnorm_add_sum(const float* y1, float s1, const float* y2, float s2, const float* w, float* resid,
+                              void* rounded, int rounded_dtype, int N, int H, float eps, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (rounded && rounded_dtype == MV_DT_BF16)
+        mv_launch(rmsnorm_add_sum_kernel<__nv_bfloat16>, N, threads, 0, stream, y1, s1, y2, s2, w, resid,
+                  (__nv_bfloat16*)rounded, H, eps);
+    else
+        mv_launch(rmsnorm_add_sum_kernel<float>, N, threads, 0, stream, y1, s1, y2, s2, w, resid, (float*)rounded, H, eps);
     return mv_launch_status();
 }
 

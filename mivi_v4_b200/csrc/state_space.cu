@@ -1,0 +1,95 @@
+// What a selective state space layer does to its projection before the recurrence:
+//   * a causal convolution along the sequence, one filter of `taps` taps per channel, with a bias, then
+//     silu; the last tap is the current token's, and before a sequence's start the input is zero.  The last
+//     taps - 1 inputs of a sequence are kept per slot, so a prompt may be cut anywhere;
+//   * the step size dt = softplus(raw + bias) per token and head, from which the recurrence's two
+//     scalars follow: log a = -e^(A_log) dt and b = dt.
+// Input: 32-bit rows of the projection, [.. | conv channels | dt heads] at given column offsets.
+// Everything is computed in 32-bit.
+#include "common.cuh"
+
+#define SP_MAX_TAPS 16
+
+// conv state [slot][taps - 1][C], oldest first.  One thread a (token, channel).
+__global__ void __launch_bounds__(256)
+causal_conv_silu_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
+                        const float* __restrict__ bias, const float* __restrict__ state,
+                        const int* __restrict__ seq_of, const int* __restrict__ cu, const int* __restrict__ slots,
+                        float* __restrict__ out, long long total, int C, int K) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int n = (int)(idx / C), c = (int)(idx - (long long)n * C);
+    const int b = seq_of[n];
+    const int li = n - cu[b];                               // place among the step's tokens of its sequence
+    const float* st = state + (size_t)mv_read_slot(slots[b]) * (K - 1) * C;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < K; ++j) {
+        const int back = K - 1 - j;                          // tap j reads the input `back` tokens ago
+        const float x = li >= back ? u[(size_t)(n - back) * ld + c] : st[(size_t)(li + j) * C + c];
+        acc = fmaf(taps[(size_t)c * K + j], x, acc);
+    }
+    out[idx] = acc / (1.0f + expf(-acc));
+}
+
+// After the step the kept inputs are the last taps - 1 of (kept inputs, the step's inputs).  One thread a
+// (sequence, channel) reads all it needs before it writes.
+__global__ void __launch_bounds__(256)
+causal_conv_state_kernel(const float* __restrict__ u, int ld, float* __restrict__ state, const int* __restrict__ cu,
+                         const int* __restrict__ slots, int C, int K) {
+    mv_pdl_begin();
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C || !mv_slot_ok(slots[b])) return;
+    const int row0 = cu[b], len = cu[b + 1] - row0;
+    if (len <= 0) return;
+    float* st = state + (size_t)slots[b] * (K - 1) * C;
+    float keep[SP_MAX_TAPS];
+    for (int s = 0; s < K - 1; ++s) {
+        const int src = s + len;                             // index into (kept inputs, step's inputs)
+        keep[s] = src < K - 1 ? st[(size_t)src * C + c] : u[(size_t)(row0 + src - (K - 1)) * ld + c];
+    }
+    for (int s = 0; s < K - 1; ++s) st[(size_t)s * C + c] = keep[s];
+}
+
+__global__ void __launch_bounds__(256)
+step_size_kernel(const float* __restrict__ raw, int ld, const float* __restrict__ dt_bias,
+                 const float* __restrict__ a_log, float* __restrict__ log_a, float* __restrict__ b_out, long long total,
+                 int H) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int n = (int)(idx / H), h = (int)(idx - (long long)n * H);
+    const float z = raw[(size_t)n * ld + h] + dt_bias[h];
+    const float dt = z > 20.f ? z : log1pf(expf(z));
+    b_out[idx] = dt;
+    log_a[idx] = -expf(a_log[h]) * dt;
+}
+
+MV_GUARD_SETTER(state_space)
+
+// u: the convolution's input columns [N, C] with row stride ld; taps [C, K]; bias [C] or null; state
+// [slots][K - 1][C]; out [N, C] dense.  Two kernels: the outputs (which read the kept inputs), then the kept
+// inputs' update.
+MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const float* bias, float* state,
+                               const int* seq_of, const int* cu, const int* slots, float* out, int N, int n_seqs,
+                               int C, int K, cudaStream_t stream) {
+    if (N <= 0 || n_seqs <= 0) return 0;
+    if (K < 1 || K > SP_MAX_TAPS || C < 1) return (int)cudaErrorInvalidValue;
+    const long long total = (long long)N * C;
+    mv_launch(causal_conv_silu_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, u, ld, taps, bias,
+              (const float*)state, seq_of, cu, slots, out, total, C, K);
+    if (K > 1)
+        mv_launch(causal_conv_state_kernel, dim3((C + 255) / 256, n_seqs), 256, 0, stream, u, ld, state, cu, slots, C, K);
+    return mv_launch_status();
+}
+
+// raw [N, H] with row stride ld; dt_bias, a_log [H]; log_a, b_out [N, H] dense.
+MV_API int mv_step_size(const float* raw, int ld, const float* dt_bias, const float* a_log, float* log_a,
+                        float* b_out, int N, int H, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const long long total = (long long)N * H;
+    mv_launch(step_size_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, raw, ld, dt_bias, a_log, log_a, b_out,
+              total, H);
+    return mv_launch_status();
+}

@@ -57,9 +57,20 @@ _SIGNATURES = {
         "mv_decay_chunks": [_I, _I],
         "mv_decay_scan_chunked": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _F, _F, _I, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I,
                                   _I, _I, _I, _P],
-        "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _P],
+        "mv_qkv_prepare_wide": [_P, _I, _P, _P, _F, _I, _P, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I, _I, _I, _I,
+                                _F, _P],
         "mv_attention_sink": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I, _I,
-                              _I, _P],
+                              _I, _I, _P],
+        "mv_embed_scaled_pos": [_P, _I, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
+        "mv_softcap": [_P, _Q, _F, _P],
+        "mv_rmsnorm_add_sum": [_P, _F, _P, _F, _P, _P, _P, _I, _I, _I, _F, _P],
+        "mv_scalar_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
+                           _P],
+        "mv_memory_gates": [_P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+        "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
+        "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+        "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
@@ -77,7 +88,7 @@ _SIGNATURES = {
                                   _P, _I, _I, _I, _F, _P, _Q, _P, _P],
         "mv_attention_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P],
         "mv_attention_sink_prefill": [_P, _P, _Q, _P, _I, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _F, _F, _I,
-                                      _I, _P],
+                                      _I, _I, _P],
         "mv_attention_decode_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _F, _I, _P, _P],
         "mv_attention_prefill_tc": [_P, _P, _Q, _P, _I, _P, _P, _P, _I, _I, _I, _I, _F, _P, _P],
     },
@@ -285,7 +296,7 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
 
 _launches = 0
 # kernels launched by one call of each entry point
-_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2}
+_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2, "mv_causal_conv_silu": 2}
 
 
 def launch_count() -> int:
@@ -362,14 +373,15 @@ def layernorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     return out
 
 
-GATE_SILU, GATE_SIGMOID = 0, 1
+GATE_SILU, GATE_SIGMOID, GATE_SILU_FIRST = 0, 1, 2
 
 
 def gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, group: int, eps: float, act: int,
                   out: torch.Tensor) -> torch.Tensor:
     """Every group of ``group`` consecutive values of a row of x [N, C] (float32) is divided by its root mean
-    square, multiplied by w[c mod len(w)] and by act(gate[n, c]): ``GATE_SILU`` or ``GATE_SIGMOID``.  ``gate``
-    (float32) may be a column slice of a wider matrix: only its rows must be contiguous."""
+    square, multiplied by w[c mod len(w)] and by act(gate[n, c]): ``GATE_SILU`` or ``GATE_SIGMOID``.  With
+    ``GATE_SILU_FIRST`` the gate comes before the norm: x * silu(gate) is divided by ITS root mean square and
+    multiplied by w.  ``gate`` (float32) may be a column slice of a wider matrix: only its rows must be contiguous."""
     N, C = x.shape
     if group < 1 or C % group:
         raise KernelError(f"gated_rmsnorm: rows of {C} values do not split into groups of {group}")
@@ -475,6 +487,168 @@ def round_rows(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def embed_scaled_pos(table: torch.Tensor, tokens: torch.Tensor, scale: float, pos_table: Optional[torch.Tensor],
+                     positions: torch.Tensor, out: torch.Tensor, rounded: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[n] = table[tokens[n]] * scale + pos_table[positions[n]] in float32 (``pos_table`` None: no position
+    vector); ``rounded`` also gets the rows in its own dtype."""
+    N, H = out.shape
+    if pos_table is not None and pos_table.dtype != table.dtype:
+        raise KernelError(f"embed: the token table is {table.dtype}, the position table {pos_table.dtype}")
+    _check(_fn("core", "mv_embed_scaled_pos")(
+        _need(table, "embedding table", None, (None, H)), _dt(table), _need(tokens, "tokens", torch.int32), float(scale),
+        _need(pos_table, "position table", None, (None, H), True), _need(positions, "positions", torch.int32),
+        _need(out, "embed out", torch.float32), _need(rounded, "embed rounded", None, (N, H), True),
+        _dt(rounded) if rounded is not None else F32, N, H, _stream()), "mv_embed_scaled_pos")
+    account(N * H * (2 * table.element_size() + 4))
+    return out
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _check(_fn("core", "mv_softcap")(_need(x, "softcap x", torch.float32), x.numel(), float(cap), _stream()), "mv_softcap")
+    account(x.numel() * 8)
+    return x
+
+
+def rmsnorm_add_sum(y1: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.Tensor, *, s1: float = 1.0,
+                    y2: Optional[torch.Tensor] = None, s2: float = 1.0, rounded: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """resid += y / sqrt(mean(y^2) + eps) * w with y = s1 * y1 (+ s2 * y2), all float32; ``rounded`` also gets
+    the completed rows in its own dtype (what the next sublayer multiplies)."""
+    N, H = y1.shape
+    _check(_fn("core", "mv_rmsnorm_add_sum")(
+        _need(y1, "rmsnorm_add_sum y1", torch.float32), float(s1), _need(y2, "rmsnorm_add_sum y2", torch.float32, (N, H), True),
+        float(s2), _need(w, "rmsnorm_add_sum weight", torch.float32, (H,)),
+        _need(resid, "residual stream", torch.float32, (N, H)), _need(rounded, "rounded rows", None, (N, H), True),
+        _dt(rounded) if rounded is not None else F32, N, H, float(eps), _stream()), "mv_rmsnorm_add_sum")
+    account(N * H * (12 + (4 if y2 is not None else 0) + (rounded.element_size() if rounded is not None else 0)))
+    return resid
+
+
+def scalar_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor,
+                state: torch.Tensor, slots: torch.Tensor, cu: torch.Tensor, out: torch.Tensor, n_seqs: int,
+                n_heads: int, dk: int, dv: int, *, heads_per_group: int = 1, skip: Optional[torch.Tensor] = None,
+                m_tok: Optional[torch.Tensor] = None, q_scale: float = 1.0) -> torch.Tensor:
+    """A matrix state per head with ONE decay per token and head: S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t
+    (+ skip_h v_t), over the step's tokens in order, from and into ``state`` [slots, heads, dv (+ 1), dk]
+    (float32).  ``log_a`` and ``b`` [N, heads] are float32 (column slices are fine); q, k [N, groups * dk]
+    with ``heads_per_group`` heads sharing a group's q and k; v [N, heads * dv].  With ``m_tok`` [N, heads] the
+    state has one more value column, the normalizer n <- a_t n + b_t k_t, and
+    o_t <- o_t / (max(|n . q_t|, exp(-m_tok)) + 1e-6).  Everything is computed in float32; the order of every
+    sum depends on dk alone, so any cut of a prompt gives the same numbers."""
+    N = out.shape[0]
+    if not 1 <= dk <= MAX_SCAN_KEY_DIM:
+        raise KernelError(f"scalar_scan: key size {dk} is outside 1..{MAX_SCAN_KEY_DIM}")
+    if heads_per_group < 1 or n_heads % heads_per_group:
+        raise KernelError(f"scalar_scan: {n_heads} heads do not split into groups of {heads_per_group}")
+    groups = n_heads // heads_per_group
+    qp, ldq = _cols(q, "scalar_scan q", N, groups * dk)
+    kp, ldk = _cols(k, "scalar_scan k", N, groups * dk)
+    vp, ldv = _cols(v, "scalar_scan v", N, n_heads * dv)
+    ap, lda = _cols(log_a, "scalar_scan log decay", N, n_heads)
+    bp, ldb = _cols(b, "scalar_scan input factor", N, n_heads)
+    norm = m_tok is not None
+    _need(state, "scalar_scan state", torch.float32, (None, n_heads, dv + (1 if norm else 0), dk))
+    _guard("core", "scalar_scan", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_scalar_scan")(
+        qp, ldq, kp, ldk, vp, ldv, ap, lda, bp, ldb, _need(skip, "scalar_scan skip", torch.float32, (n_heads,), True),
+        _need(m_tok, "scalar_scan m", torch.float32, (N, n_heads), True), float(q_scale), state.data_ptr(),
+        _need(slots, "slots", torch.int32), _need(cu, "cu", torch.int32),
+        _need(out, "scalar_scan out", torch.float32, (N, n_heads * dv)), int(n_seqs), n_heads, int(heads_per_group), dk, dv,
+        int(norm), _stream()), "mv_scalar_scan")
+    account(N * n_heads * (2 * dk + 2 * dv) * 4 + 2 * n_seqs * n_heads * dk * dv * 4, 4 * N * n_heads * dk * dv)
+    return out
+
+
+def memory_gates(zi: torch.Tensor, zf: torch.Tensor, bi: torch.Tensor, bf: torch.Tensor, cap: float,
+                 m_state: torch.Tensor, slots: torch.Tensor, cu: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor,
+                 m_tok: torch.Tensor, n_seqs: int, n_heads: int) -> None:
+    """The log gates of a matrix memory: i = cap tanh((zi + bi) / cap), f = log sigmoid(cap tanh((zf + bf) / cap)),
+    the running maximum m_t = max(f_t + m_(t-1), i_t) from and into ``m_state`` [slots, heads], and from them
+    log_a = f + m_(t-1) - m_t, b = exp(i - m_t), m_tok = m_t, all float32 [N, heads]."""
+    N = log_a.shape[0]
+    ip, ldi = _cols(zi, "memory_gates input gate", N, n_heads)
+    fp, ldf = _cols(zf, "memory_gates forget gate", N, n_heads)
+    _guard("core", "scalar_scan", log_a.device, n_slots=m_state.shape[0])
+    _check(_fn("core", "mv_memory_gates")(
+        ip, ldi, fp, ldf, _need(bi, "input gate bias", torch.float32, (n_heads,)),
+        _need(bf, "forget gate bias", torch.float32, (n_heads,)), float(cap),
+        _need(m_state, "memory_gates m", torch.float32, (None, n_heads)), _need(slots, "slots", torch.int32),
+        _need(cu, "cu", torch.int32), _need(log_a, "log_a", torch.float32, (N, n_heads)),
+        _need(b, "b", torch.float32, (N, n_heads)), _need(m_tok, "m_tok", torch.float32, (N, n_heads)), int(n_seqs),
+        n_heads, _stream()), "mv_memory_gates")
+    account(N * n_heads * 20)
+
+
+def causal_conv_silu(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                     seq_of: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, n_seqs: int) -> torch.Tensor:
+    """out = silu(bias + sum_j taps[:, j] * u[t - (K - 1) + j]) per channel along each sequence (the last tap is the
+    current token's; zeros before a sequence's start), float32.  ``u`` [N, C] may be a column slice; ``state``
+    [slots, K - 1, C] holds each sequence's last K - 1 inputs and is brought up to date."""
+    N, C = out.shape
+    K = taps.shape[1]
+    if not 1 <= K <= MAX_CONV_K:
+        raise KernelError(f"causal_conv_silu: {K} taps are outside 1..{MAX_CONV_K}")
+    up, ldu = _cols(u, "causal_conv_silu input", N, C)
+    _guard("core", "state_space", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_causal_conv_silu")(
+        up, ldu, _need(taps, "conv taps", torch.float32, (C, K)), _need(bias, "conv bias", torch.float32, (C,), True),
+        _need(state, "conv state", torch.float32, (None, max(K - 1, 0), C)) if K > 1 else None,
+        _need(seq_of, "seq_of", torch.int32), _need(cu, "cu", torch.int32), _need(slots, "slots", torch.int32),
+        _need(out, "causal_conv_silu out", torch.float32), N, int(n_seqs), C, K, _stream()), "mv_causal_conv_silu")
+    account(N * C * 8 + 2 * n_seqs * (K - 1) * C * 4, 2 * N * C * K)
+    return out
+
+
+def step_size(raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor) -> None:
+    """dt = softplus(raw + dt_bias) per token and head; b = dt, log_a = -exp(a_log) * dt; float32 [N, heads]."""
+    N, H = log_a.shape
+    rp, ldr = _cols(raw, "step_size raw", N, H)
+    _check(_fn("core", "mv_step_size")(
+        rp, ldr, _need(dt_bias, "dt bias", torch.float32, (H,)), _need(a_log, "A_log", torch.float32, (H,)),
+        _need(log_a, "log_a", torch.float32), _need(b, "b", torch.float32, (N, H)), N, H, _stream()), "mv_step_size")
+    account(N * H * 12)
+
+
+MAX_EXPERTS = 1024
+
+
+def route(z: torch.Tensor, dense: torch.Tensor, pick: torch.Tensor, pick_w: torch.Tensor, n_experts: int,
+          n_groups: int, keep: int, top: int, shared_gate: bool) -> None:
+    """Router of a mixture of experts from float32 logits ``z`` [N, experts (+ 1)]: scores sigmoid(z); the experts
+    form ``n_groups`` equal groups of neighbours whose score is the sum of their two largest scores; among the
+    experts of the ``keep`` best groups the ``top`` largest are chosen, with weights score / (sum of the chosen
+    scores + 1e-20).  ``dense`` [N, experts (+ 1)] gets a row of weights (zero where not chosen; with
+    ``shared_gate`` the last column is sigmoid of the last logit), ``pick`` / ``pick_w`` [N, top] the lists."""
+    N = dense.shape[0]
+    E = int(n_experts)
+    cols = E + (1 if shared_gate else 0)
+    if (E < 1 or E > MAX_EXPERTS or n_groups < 1 or E % n_groups or not 1 <= keep <= n_groups or not 1 <= top <= 32
+            or top > keep * (E // n_groups)):
+        raise KernelError(f"route: {E} experts in {n_groups} groups, {keep} groups kept, {top} chosen: not a routing "
+                          f"this kernel takes (at most {MAX_EXPERTS} experts, 32 chosen)")
+    zp, ldz = _cols(z, "router logits", N, cols)
+    _check(_fn("core", "mv_route")(
+        zp, ldz, _need(dense, "route weights", torch.float32, (N, cols)), _need(pick, "route picks", torch.int32, (N, top)),
+        _need(pick_w, "route pick weights", torch.float32, (N, top)), N, E, int(n_groups), int(keep), int(top),
+        int(bool(shared_gate)), _stream()), "mv_route")
+    account(N * cols * 8)
+
+
+def routed_glu(gu: torch.Tensor, dense: torch.Tensor, hid: torch.Tensor, n_experts: int, ff: int, shared_ff: int) -> torch.Tensor:
+    """hid[n, c] = weight(n, expert of column c) * silu(gate[n, c]) * up[n, c] over the columns of all experts end to
+    end (then a shared expert's), from ``gu`` [N, 2 * F] float32 (all gates, then all ups) and the router's
+    dense weights; nothing is computed where the weight is zero."""
+    N, F = hid.shape
+    if F != n_experts * ff + shared_ff:
+        raise KernelError(f"routed_glu: {F} columns for {n_experts} experts of {ff} and a shared one of {shared_ff}")
+    _check(_fn("core", "mv_routed_glu")(
+        _need(gu, "routed_glu input", torch.float32, (N, 2 * F)),
+        _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0))),
+        _need(hid, "routed_glu out"), _dt(hid), N, int(n_experts), int(ff), int(shared_ff), _stream()), "mv_routed_glu")
+    account(N * F * (8 + hid.element_size()))
+    return hid
+
+
 MAX_SCAN_KEY_DIM = 256
 SCAN_ACT_NONE, SCAN_ACT_SILU = 0, 1
 SCAN_CHUNKED_FROM = 16          # a step whose longest sequence brings this many tokens walks them in chunks
@@ -558,11 +732,12 @@ def _check_kv_wide(pool: torch.Tensor, nkv: int, page_size: int, dk: int, dv: in
 def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float,
                      rot_dims: int, inv_freq: Optional[torch.Tensor], positions, seq_of, page_table,
                      pool: torch.Tensor, page_size: int, q_out: torch.Tensor, nh: int, nkv: int, dk: int,
-                     dv: int) -> torch.Tensor:
+                     dv: int, *, per_head: bool = False, amplitude: float = 1.0) -> torch.Tensor:
     """From a row [q | k | v | ...] of a fused projection (float32, any row stride): root-mean-square norm over
-    the whole of q and the whole of k (weights wq [nh * dk], wk [nkv * dk]; None: no norm), rotation of the
-    first ``rot_dims`` elements of every head (element i with i + rot_dims / 2, angle pos * inv_freq[i]), q
-    out in the model's dtype, k and v into the token's row of its page."""
+    the whole of q and the whole of k (weights wq [nh * dk], wk [nkv * dk]; None: no norm), or with
+    ``per_head`` over every head by itself (weights wq, wk [dk], shared by the heads); rotation of the
+    first ``rot_dims`` elements of every head (element i with i + rot_dims / 2, angle pos * inv_freq[i], cos and
+    sin times ``amplitude``), q out in the model's dtype, k and v into the token's row of its page."""
     N = q_out.shape[0]
     need = nh * dk + nkv * (dk + dv)
     if (not proj.is_cuda or proj.dtype != torch.float32 or proj.dim() != 2 or proj.shape[0] != N or proj.shape[1] < need
@@ -576,13 +751,13 @@ def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optiona
         raise KernelError(f"qkv_prepare_wide: cache is {pool.dtype} but q is {q_out.dtype}")
     _guard("core", "attention_sink", proj.device, n_pages=pool.shape[0])
     _check(_fn("core", "mv_qkv_prepare_wide")(
-        proj.data_ptr(), proj.stride(0), _need(wq, "q norm weight", torch.float32, (nh * dk,), True),
-        _need(wk, "k norm weight", torch.float32, (nkv * dk,), True), float(eps), int(rot_dims),
+        proj.data_ptr(), proj.stride(0), _need(wq, "q norm weight", torch.float32, (dk if per_head else nh * dk,), True),
+        _need(wk, "k norm weight", torch.float32, (dk if per_head else nkv * dk,), True), float(eps), int(rot_dims),
         _need(inv_freq, "inv_freq", torch.float32, (rot_dims // 2,), rot_dims == 0),
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size, _need(pool, "cache pool"),
-        pool.stride(0), _need(q_out, "q out", None, (N, nh * dk)), _dt(q_out), N, nh, nkv, dk, dv, _stream()),
-        "mv_qkv_prepare_wide")
+        pool.stride(0), _need(q_out, "q out", None, (N, nh * dk)), _dt(q_out), N, nh, nkv, dk, dv, int(bool(per_head)),
+        float(amplitude), _stream()), "mv_qkv_prepare_wide")
     account(N * need * 4 + N * (nh * dk + nkv * (dk + dv)) * q_out.element_size())
     return q_out
 
@@ -590,12 +765,13 @@ def qkv_prepare_wide(proj: torch.Tensor, wq: Optional[torch.Tensor], wk: Optiona
 def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, positions, seq_of,
                    out: torch.Tensor, nh: int, nkv: int, dk: int, dv: int, scale: float, *, softcap: float = 0.0,
                    window: int = 0, keep_first: int = 0, sinks: Optional[torch.Tensor] = None,
-                   gate: Optional[torch.Tensor] = None, head_tile: int = 0) -> torch.Tensor:
+                   gate: Optional[torch.Tensor] = None, head_tile: int = 0, chunk: int = 0) -> torch.Tensor:
     """Causal softmax attention of every token of the step over its sequence's cache (which already holds the
     step's own keys), keys of size dk and values of size dv.  ``softcap`` c > 0: s <- c tanh(s / c).  ``window``
     w > 0 with ``keep_first`` f: query i reads key j if i - j < w or j < f.  ``sinks`` [nh]: exp(sink) joins
     each head's denominator.  ``gate``: float32 logits [N, nh] (a column slice is fine); the head's output is
-    multiplied by sigmoid(gate).  ``head_tile``: how many query heads of a kv head share a block and its loads
+    multiplied by sigmoid(gate).  ``chunk`` c > 0 (instead of a window): query i reads key j <= i only if
+    i // c == j // c.  ``head_tile``: how many query heads of a kv head share a block and its loads
     (1, 2 or 4; 0: the kernel chooses by the step's size)."""
     N = q.shape[0]
     if not (1 <= dk <= MAX_HEAD_DIM and 1 <= dv <= MAX_HEAD_DIM):
@@ -613,7 +789,7 @@ def attention_sink(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_tab
         _need(positions, "positions", torch.int32), _need(seq_of, "seq_of", torch.int32),
         _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
         _dt(q), N, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(head_tile),
-        _stream()), "mv_attention_sink")
+        int(chunk), _stream()), "mv_attention_sink")
     return out
 
 
@@ -627,7 +803,8 @@ def attention_sink_prefill_supported(dtype: torch.dtype, dk: int, dv: int) -> bo
 def attention_sink_prefill(q: torch.Tensor, pool: torch.Tensor, page_size: int, page_table, cu, starts,
                            out: torch.Tensor, n_seqs: int, nh: int, nkv: int, dk: int, dv: int, scale: float, *,
                            softcap: float = 0.0, window: int = 0, keep_first: int = 0,
-                           sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                           chunk: int = 0) -> torch.Tensor:
     """:func:`attention_sink` for a step with many query tokens, on the tensor cores (bfloat16, key and value
     sizes 16..128 in steps of 16).  The step's tokens are packed sequence by sequence (``cu``), sequence b
     starting at position ``starts[b]``."""
@@ -647,7 +824,7 @@ def attention_sink_prefill(q: torch.Tensor, pool: torch.Tensor, page_size: int, 
         _need(page_table, "page table", torch.int32), page_table.shape[1], page_size,
         _need(cu, "cu", torch.int32), _need(starts, "starts", torch.int32),
         _need(sinks, "sinks", torch.float32, (nh,), True), gp, ldg, _need(out, "attention out", None, (N, nh * dv)),
-        N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), _stream()),
+        N, n_seqs, nh, nkv, dk, dv, float(scale), float(softcap), int(window), int(keep_first), int(chunk), _stream()),
         "mv_attention_sink_prefill")
     return out
 

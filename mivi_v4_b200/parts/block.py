@@ -1,9 +1,12 @@
 """Arrangements of a layer's parts."""
 from __future__ import annotations
 
+import torch
+
+from ..ops import kernels as K
 from ..ops.kernels import profile_stage
 from .base import Part
-from .norm import LayerNorm
+from .norm import LayerNorm, RMSNorm
 from .registry import register
 
 
@@ -143,3 +146,81 @@ class PreNormOptionalBlock(Part):
                     step.handed = (nxt, out)
                 else:
                     self.token_input.forward(resid, step)
+
+
+@register("block", "postnorm")
+class PostNormBlock(Part):
+    """x += norm1(mixer(x)); then, if the layer has a feed-forward, x += norm2(feed_forward(x)): the norms sit on
+    the sublayers' OUTPUTS and the sublayers read the stream itself (rounded to the model's dtype where that is
+    narrower).  The norms are root-mean-square norms.  One kernel per sublayer adds a mixer's branches (a mixer
+    with ``forward_sum`` gives them apart, with their factors), norms the sum, adds it to the float32 stream and
+    writes the rounded rows that the next sublayer multiplies."""
+
+    nested_roles = {"mixer": "mixer", "mixer_norm": "norm", "ffn": "feed_forward", "ffn_norm": "norm"}
+
+    def __init__(self, mixer, mixer_norm, ffn=None, ffn_norm=None):
+        if (ffn is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together or not at all")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and not isinstance(norm, RMSNorm):
+                raise ValueError("the norms of a postnorm block are rmsnorm parts")
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm = mixer, mixer_norm, ffn, ffn_norm
+
+    def nested(self):
+        parts = {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "ffn": self.ffn, "ffn_norm": self.ffn_norm}
+        return {k: v for k, v in parts.items() if v is not None}
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def entry_link(self, step):
+        """No product carries this block's norms; the method is there so that the model tells ``forward`` which
+        block runs next (``after``)."""
+        return None
+
+    def _run(self, part, u, step, *args):
+        """The sublayer's result in a buffer of its own, as a list of (rows, factor)."""
+        N = u.shape[0]
+        if hasattr(part, "forward_sum"):
+            return part.forward_sum(u, step, *args)
+        y = self.scratch(step, "y", (N, self.mixer_norm.dim), torch.float32)
+        if getattr(part, "overwrites", False):
+            part.forward(u, y, step, *args, accumulate=False)
+        else:
+            y.zero_()                                 # a part that can only add
+            part.forward(u, y, step, *args)
+        return [(y, 1.0)]
+
+    def _add(self, branches, norm, resid, rounded):
+        (y1, s1), rest = branches[0], branches[1:]
+        if len(rest) > 1:
+            raise ValueError("at most two branches are summed in the norm's kernel")
+        y2, s2 = rest[0] if rest else (None, 1.0)
+        K.rmsnorm_add_sum(y1, norm.weight, norm.eps, resid, s1=s1, y2=y2, s2=s2, rounded=rounded)
+
+    def forward(self, resid, step, view, after=None) -> None:
+        N, H = resid.shape
+        narrow = step.dtype != torch.float32
+        handed, step.handed = getattr(step, "handed", None), None
+        if not narrow:
+            u = resid                                   # the sublayers multiply the stream itself
+        elif handed is not None and handed[0] == "stream":
+            u = handed[1]
+        else:
+            u = K.round_rows(resid, step.ws.get("stream_rounded", (N, H), step.dtype))
+        rounded = step.ws.get("stream_rounded", (N, H), step.dtype) if narrow else None
+        last = self.ffn is None
+        with profile_stage("mixer " + getattr(self.mixer, "kind", "?")):
+            branches = self._run(self.mixer, u, step, view)
+        with profile_stage("norm"):
+            # the rounded rows are wanted by this block's feed-forward, or by the next block of this kind
+            want = narrow and (not last or isinstance(after, PostNormBlock))
+            self._add(branches, self.mixer_norm, resid, rounded if want else None)
+        if not last:
+            with profile_stage("feed_forward " + getattr(self.ffn, "kind", "?")):
+                branches = self._run(self.ffn, rounded if narrow else resid, step)
+            with profile_stage("norm"):
+                want = narrow and isinstance(after, PostNormBlock)
+                self._add(branches, self.ffn_norm, resid, rounded if want else None)
+        if narrow and isinstance(after, PostNormBlock):
+            step.handed = ("stream", rounded)

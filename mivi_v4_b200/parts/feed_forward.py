@@ -21,6 +21,8 @@ class SwiGLU(Part):
     which lets the tensor-core kernels apply the activation in their
     epilogue; else end to end."""
 
+    overwrites = True            # forward(..., accumulate=False) writes its result instead of adding it
+
     def __init__(self, hidden: int, ff: int):
         self.hidden, self.ff = int(hidden), int(ff)
 
@@ -45,7 +47,7 @@ class SwiGLU(Part):
         n = step.n_tokens
         return (bool(self.group) and norm_link_ok(n, self.w13, step.dtype)), norm_link_ok(n, self.w2, step.dtype, emits=True)
 
-    def forward(self, g, resid, step, scale=None, emit=None) -> None:
+    def forward(self, g, resid, step, scale=None, emit=None, accumulate: bool = True) -> None:
         N = g.shape[0]
         h = self.scratch(step, "ffh", (N, self.ff), step.dtype)
         if self.group and tensor_core_ok(g, self.w13):
@@ -54,7 +56,7 @@ class SwiGLU(Part):
             gu = self.scratch(step, "proj", (N, 2 * self.ff), torch.float32)
             linear(g, self.w13, gu, scale=scale)
             K.swiglu(gu, h, self.group)
-        linear(h, self.w2, resid, accumulate=True, emit=emit)
+        linear(h, self.w2, resid, accumulate=accumulate, emit=emit)
 
 
 @register("feed_forward", "clamped_glu")
@@ -85,3 +87,70 @@ class ClampedGLU(Part):
         h = self.scratch(step, "ffh", (N, self.ff), step.dtype)
         K.glu_clamped(gu, h, self.limit, self.alpha)
         linear(h, self.w_down, resid, accumulate=True)
+
+
+@register("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """Mixture of experts with sigmoid scores: every expert is W_down (silu(W_gate h) * (W_up h)) without
+    biases; router logits z = W_router h in float32, scores s = sigmoid(z); the experts form ``n_groups`` equal
+    groups of neighbours, a group's score is the sum of its two largest scores, and only experts of the
+    ``keep_groups`` best groups can be chosen; the ``top`` largest scores among them are chosen and weigh their
+    experts by s / (sum of the chosen s + 1e-20).  With ``shared_ff`` > 0 a shared expert of that width runs for
+    every token and is added times sigmoid(w_sg . h).
+
+    All experts' gate and up matrices are laid end to end (the shared expert's last), so that one product yields
+    every expert's pre-activations; the gated activation is multiplied by the router's weight before it is
+    rounded (zero where an expert was not chosen: nothing is computed there), and one product with the down
+    matrices side by side sums the chosen experts.  No decision is taken on the host."""
+
+    overwrites = True
+
+    def __init__(self, hidden: int, n_experts: int, ff: int, top: int, n_groups: int = 1, keep_groups: int = 1,
+                 shared_ff: int = 0):
+        if n_experts < 1 or n_experts > K.MAX_EXPERTS or n_groups < 1 or n_experts % n_groups:
+            raise ValueError(f"{n_experts} experts do not form {n_groups} equal groups (at most {K.MAX_EXPERTS} experts)")
+        if not 1 <= keep_groups <= n_groups or not 1 <= top <= min(32, keep_groups * (n_experts // n_groups)):
+            raise ValueError(f"{top} experts cannot be chosen from {keep_groups} of {n_groups} groups of "
+                             f"{n_experts // n_groups} (at most 32)")
+        self.hidden, self.E, self.ff, self.top = int(hidden), int(n_experts), int(ff), int(top)
+        self.n_groups, self.keep, self.shared_ff = int(n_groups), int(keep_groups), int(shared_ff)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, F = self.hidden, self.ff
+        specs = {"router": ParamSpec((self.E, H))}
+        for e in range(self.E):
+            specs.update({f"e{e}.gate": ParamSpec((F, H)), f"e{e}.up": ParamSpec((F, H)), f"e{e}.down": ParamSpec((H, F))})
+        if self.shared_ff:
+            S = self.shared_ff
+            specs.update({"shared.gate": ParamSpec((S, H)), "shared.up": ParamSpec((S, H)), "shared.down": ParamSpec((H, S)),
+                          "shared.sg": ParamSpec((1, H))})
+        return specs
+
+    def load(self, t) -> None:
+        names = [f"e{e}." for e in range(self.E)] + (["shared."] if self.shared_ff else [])
+        mats = [t[n + "gate"] for n in names] + [t[n + "up"] for n in names] + [t[n + "down"] for n in names]
+        if len({m.dtype for m in mats}) != 1:
+            t = {k: v.float() for k, v in t.items()}
+        self.w_gu = torch.cat([t[n + "gate"] for n in names] + [t[n + "up"] for n in names], dim=0).contiguous()
+        self.w_down = torch.cat([t[n + "down"] for n in names], dim=1).contiguous()
+        rows = [t["router"]] + ([t["shared.sg"]] if self.shared_ff else [])
+        pad = -sum(r.shape[0] for r in rows) % 16
+        if pad:
+            rows.append(torch.zeros((pad, self.hidden), dtype=rows[0].dtype, device=rows[0].device))
+        self.w_router = torch.cat(rows, dim=0).contiguous()
+
+    def forward(self, g, resid, step, accumulate: bool = True) -> None:
+        N = g.shape[0]
+        E, F = self.E, self.E * self.ff + self.shared_ff
+        cols = E + (1 if self.shared_ff else 0)
+        z = self.scratch(step, "z", (N, self.w_router.shape[0]), torch.float32)
+        linear(g, self.w_router, z)
+        dense = self.scratch(step, "route", (N, cols), torch.float32)
+        pick = self.scratch(step, "pick", (N, self.top), torch.int32)
+        pick_w = self.scratch(step, "pick_w", (N, self.top), torch.float32)
+        K.route(z[:, :cols], dense, pick, pick_w, E, self.n_groups, self.keep, self.top, bool(self.shared_ff))
+        gu = self.scratch(step, "proj", (N, 2 * F), torch.float32)
+        linear(g, self.w_gu, gu)
+        h = self.scratch(step, "ffh", (N, F), step.dtype)
+        K.routed_glu(gu, dense, h, E, self.ff, self.shared_ff)
+        linear(h, self.w_down, resid, accumulate=accumulate)

@@ -8,6 +8,7 @@ import torch
 
 from ..cache.needs import KVNeed, StateNeed
 from ..ops import kernels as K
+from ..ops.kernels import profile_stage
 from ..ops.linear import (conv_rows_grouped, heads_fused_ok, linear, linear_heads, linear_shortconv_decode, norm_link_ok,
                           shortconv_decode_fused_ok)
 from .base import Part
@@ -304,13 +305,18 @@ class SinkAttention(Part):
     of ``window`` tokens (0: none) that also keeps the sequence's first ``keep_first`` tokens; with ``sink`` a
     learned number per head whose exponential joins the softmax's denominator; with ``gated`` each head's
     output times sigmoid of one projection of the layer's input per head; then the out projection.  Scores
-    and softmax are float32."""
+    and softmax are float32.  ``norm_per_head``: the q and k norms run over every head by itself, with one
+    weight [key_dim] shared by the heads.  ``chunk`` c > 0 (instead of a window): token i reads token j <= i
+    only if i // c == j // c, chunks counted from the sequence's first position.  A position part with an
+    ``amplitude()`` has its cos and sin multiplied by it."""
 
     nested_roles = {"position": "position"}
+    overwrites = True            # forward(..., accumulate=False) writes its result instead of adding it
 
     def __init__(self, hidden: int, n_heads: int, n_kv_heads: int, key_dim: int, value_dim: int, scale: float,
                  position, softcap: float = 0.0, window: int = 0, keep_first: int = 0,
-                 qk_norm_eps: Optional[float] = None, sink: bool = True, gated: bool = True):
+                 qk_norm_eps: Optional[float] = None, sink: bool = True, gated: bool = True,
+                 norm_per_head: bool = False, chunk: int = 0):
         if n_kv_heads < 1 or n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads are not a multiple of {n_kv_heads} kv heads")
         if not (1 <= key_dim <= K.MAX_HEAD_DIM and 1 <= value_dim <= K.MAX_HEAD_DIM):
@@ -320,6 +326,9 @@ class SinkAttention(Part):
         self.window, self.keep_first = int(window), int(keep_first) if window else 0
         self.qk_norm_eps = None if qk_norm_eps is None else float(qk_norm_eps)
         self.sink, self.gated, self.position = bool(sink), bool(gated), position
+        self.norm_per_head, self.chunk = bool(norm_per_head), int(chunk)
+        if self.chunk < 0 or (self.chunk and self.window):
+            raise ValueError("a chunked mask is a size > 0 and comes instead of a window")
         self.rot_dims = 0
         if isinstance(position, Rope):
             if position.style != "half_split" or position.head_dim > self.dk:
@@ -336,8 +345,8 @@ class SinkAttention(Part):
         specs = {"q": ParamSpec((nh * dk, H)), "k": ParamSpec((nkv * dk, H)), "v": ParamSpec((nkv * dv, H)),
                  "o": ParamSpec((H, nh * dv))}
         if self.qk_norm_eps is not None:
-            specs["q.norm"] = ParamSpec((nh * dk,), "vector", "norm")
-            specs["k.norm"] = ParamSpec((nkv * dk,), "vector", "norm")
+            specs["q.norm"] = ParamSpec((dk if self.norm_per_head else nh * dk,), "vector", "norm")
+            specs["k.norm"] = ParamSpec((dk if self.norm_per_head else nkv * dk,), "vector", "norm")
         if self.sink:
             specs["sink"] = ParamSpec((nh,), "vector", "bias")
         if self.gated:
@@ -350,9 +359,9 @@ class SinkAttention(Part):
         self.q_norm, self.k_norm, self.sinks = t.get("q.norm"), t.get("k.norm"), t.get("sink")
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.keep_first)
+        return KVNeed(self.nkv, self.dk, self.window, 0 if self.dv == self.dk else self.dv, self.keep_first, self.chunk)
 
-    def forward(self, u, resid, step, view) -> None:
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
         N = u.shape[0]
         nh, nkv, dk, dv = self.nh, self.nkv, self.dk, self.dv
         proj = self.scratch(step, "proj", (N, self.w_qkvg.shape[0]), torch.float32)
@@ -361,11 +370,12 @@ class SinkAttention(Part):
         q = self.scratch(step, "q", (N, nh * dk), step.dtype)
         K.qkv_prepare_wide(proj, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, self.rot_dims,
                            rot[0] if rot is not None else None, step.positions, step.seq_of, view.page_table,
-                           view.pool, view.page_size, q, nh, nkv, dk, dv)
+                           view.pool, view.page_size, q, nh, nkv, dk, dv, per_head=self.norm_per_head,
+                           amplitude=float(getattr(self.position, "amplitude", lambda: 1.0)()) if self.rot_dims else 1.0)
         o = self.scratch(step, "mix", (N, nh * dv), step.dtype)
         g0 = nh * dk + nkv * (dk + dv)
         extras = dict(softcap=self.softcap, window=self.window, keep_first=self.keep_first, sinks=self.sinks,
-                      gate=proj[:, g0:g0 + nh] if self.gated else None)
+                      gate=proj[:, g0:g0 + nh] if self.gated else None, chunk=self.chunk)
         # few query tokens, or many sequences with a token or two each: every query token on its own
         few = N <= K.DECODE_ATTENTION_MAX_TOKENS or step.max_len <= K.DECODE_ATTENTION_MAX_QUERIES
         if not few and K.attention_sink_prefill_supported(step.dtype, dk, dv):
@@ -375,7 +385,7 @@ class SinkAttention(Part):
             K.attention_sink(q, view.pool, view.page_size, view.page_table, step.positions, step.seq_of, o, nh, nkv,
                              dk, dv, self.scale, **extras)
         if K.profiling_on():
-            reach = (self.window + self.keep_first) if self.window else None
+            reach = (self.window + self.keep_first) if self.window else (self.chunk or None)
             pairs = sum(sum(min(s + i + 1, reach) if reach else s + i + 1 for i in range(n))
                         for s, n in zip(step.host_starts, step.host_lens))
             # keys and values: every query reads its own in a step of few tokens, a sequence's tile shares them otherwise
@@ -383,4 +393,190 @@ class SinkAttention(Part):
                                          for s, n in zip(step.host_starts, step.host_lens))
             K.account(nkv * (dk + dv) * view.pool.element_size() * rows + N * nh * (dk + dv) * q.element_size(),
                       2 * nh * (dk + dv) * pairs)
-        linear(o, self.w_o, resid, accumulate=True)
+        linear(o, self.w_o, resid, accumulate=accumulate)
+
+
+@register("mixer", "mamba2")
+class Mamba2(Part):
+    """Selective state space layer in its scalar-decay form (Dao and Gu, "Transformers are SSMs: Generalized
+    Models and Efficient Algorithms Through Structured State Space Duality"): one projection of the input, laid
+    out [z: inner | x: inner | B: groups * state | C: groups * state | dt: heads] with inner = heads * value_dim;
+    x, B and C pass a causal convolution of ``conv`` taps per channel (with bias) and silu;
+    dt = softplus(dt + dt_bias); per head (head h reads group h // (heads / groups))
+    S <- exp(-exp(A_log_h) dt) S + dt B x^T, y = S^T C + D_h x; y * silu(z) is divided by its root mean
+    square in ``norm_groups`` equal parts and multiplied by ``norm``; then the out projection.  The state
+    [heads, value_dim, state] and the convolution's last conv - 1 inputs are float32 per sequence and start
+    at zero; decay, step size, state and sums are float32 in every run."""
+
+    overwrites = True
+
+    def __init__(self, hidden: int, n_heads: int, value_dim: int, state: int, groups: int, conv: int, norm_groups: int,
+                 eps: float):
+        if n_heads % groups:
+            raise ValueError(f"{n_heads} heads are not a multiple of {groups} groups")
+        if (n_heads * value_dim) % norm_groups:
+            raise ValueError(f"{n_heads * value_dim} channels do not split into {norm_groups} parts for the norm")
+        if not 1 <= conv <= K.MAX_CONV_K:
+            raise ValueError(f"convolution width {conv} is outside 1..{K.MAX_CONV_K}")
+        if not 1 <= state <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"state size {state} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        self.hidden, self.nh, self.dv, self.state, self.groups = int(hidden), int(n_heads), int(value_dim), int(state), int(groups)
+        self.conv, self.norm_groups, self.eps = int(conv), int(norm_groups), float(eps)
+        self.inner = self.nh * self.dv
+        self.channels = self.inner + 2 * self.groups * self.state
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, nh = self.hidden, self.nh
+        return {"in": ParamSpec((2 * self.inner + 2 * self.groups * self.state + nh, H)),
+                "conv": ParamSpec((self.channels, self.conv), "vector", "conv"),
+                "conv.b": ParamSpec((self.channels,), "vector", "bias"),
+                "dt_bias": ParamSpec((nh,), "vector", "bias"), "A_log": ParamSpec((nh,), "vector", "bias"),
+                "D": ParamSpec((nh,), "vector", "norm"), "norm": ParamSpec((self.inner,), "vector", "norm"),
+                "o": ParamSpec((H, self.inner))}
+
+    def load(self, t) -> None:
+        self.rows = t["in"].shape[0]
+        self.w_in = _fuse_rows([t["in"]])
+        self.taps, self.b_conv = t["conv"].contiguous(), t["conv.b"]
+        self.dt_bias, self.a_log, self.skip, self.norm, self.w_o = t["dt_bias"], t["A_log"], t["D"], t["norm"], t["o"]
+
+    def cache_need(self):
+        return [StateNeed((self.nh, self.dv, self.state)), StateNeed((self.conv - 1, self.channels))]
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N = u.shape[0]
+        nh, inner, gn = self.nh, self.inner, self.groups * self.state
+        ssm, conv = view
+        proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
+        linear(u, self.w_in, proj)
+        xbc = self.scratch(step, "xbc", (N, self.channels), torch.float32)
+        K.causal_conv_silu(proj[:, inner:inner + self.channels], self.taps, self.b_conv, conv.state, step.seq_of, step.cu,
+                           step.slots, xbc, step.n_seqs)
+        log_a = self.scratch(step, "log_a", (N, nh), torch.float32)
+        b = self.scratch(step, "b", (N, nh), torch.float32)
+        K.step_size(proj[:, inner + self.channels:inner + self.channels + nh], self.dt_bias, self.a_log, log_a, b)
+        y = self.scratch(step, "y", (N, inner), torch.float32)
+        K.scalar_scan(xbc[:, inner + gn:inner + 2 * gn], xbc[:, inner:inner + gn], xbc[:, :inner], log_a, b, ssm.state,
+                      step.slots, step.cu, y, step.n_seqs, nh, self.state, self.dv, heads_per_group=nh // self.groups,
+                      skip=self.skip)
+        g = self.scratch(step, "mix", (N, inner), step.dtype)
+        K.gated_rmsnorm(y, proj[:, :inner], self.norm, inner // self.norm_groups, self.eps, K.GATE_SILU_FIRST, g)
+        linear(g, self.w_o, resid, accumulate=accumulate)
+
+
+@register("mixer", "matrix_memory")
+class MatrixMemory(Part):
+    """Matrix memory with exponential gates (the mLSTM of Beck et al., "xLSTM: Extended Long Short-Term Memory"):
+    q = W_q h / sqrt(key_dim), k = W_k h, v = W_v h per head; log gates i = cap tanh((W_i h + b_i) / cap) and
+    f = log sigmoid(cap tanh((W_f h + b_f) / cap)) per head; with the running maximum m_t = max(f_t + m_(t-1), i_t)
+    (m before the first token is 0) S <- e^(f + m_(t-1) - m_t) S + e^(i - m_t) k v^T, n likewise with k alone,
+    o = S^T q / (max(|n . q|, e^(-m_t)) + 1e-6); each head's o is divided by its root mean square, the heads
+    together are multiplied by ``norm`` and by sigmoid(W_g h); then the out projection.  S and n
+    ([heads, value_dim + 1, key_dim], n as the last column) and m [heads] are float32 per sequence and start at
+    zero; gates, maxima, state and sums are float32 in every run."""
+
+    overwrites = True
+
+    def __init__(self, hidden: int, n_heads: int, key_dim: int, value_dim: int, gate_cap: float, eps: float):
+        if not 1 <= key_dim <= K.MAX_SCAN_KEY_DIM:
+            raise ValueError(f"key size {key_dim} is outside 1..{K.MAX_SCAN_KEY_DIM}")
+        if gate_cap <= 0:
+            raise ValueError(f"the gates' cap must be positive, got {gate_cap}")
+        self.hidden, self.nh, self.dk, self.dv = int(hidden), int(n_heads), int(key_dim), int(value_dim)
+        self.cap, self.eps = float(gate_cap), float(eps)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        H, nh, qk, vv = self.hidden, self.nh, self.nh * self.dk, self.nh * self.dv
+        return {"q": ParamSpec((qk, H)), "k": ParamSpec((qk, H)), "v": ParamSpec((vv, H)), "g": ParamSpec((vv, H)),
+                "o": ParamSpec((H, vv)), "norm": ParamSpec((vv,), "vector", "norm"),
+                "i": ParamSpec((nh, H)), "i.b": ParamSpec((nh,), "vector", "bias"),
+                "f": ParamSpec((nh, H)), "f.b": ParamSpec((nh,), "vector", "bias")}
+
+    def load(self, t) -> None:
+        self.w_all = _fuse_rows([t["q"], t["k"], t["v"], t["g"], t["i"], t["f"]])
+        self.b_i, self.b_f, self.norm, self.w_o = t["i.b"], t["f.b"], t["norm"], t["o"]
+
+    def cache_need(self):
+        return [StateNeed((self.nh, self.dv + 1, self.dk)), StateNeed((self.nh,))]
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        N = u.shape[0]
+        nh, qk, vv = self.nh, self.nh * self.dk, self.nh * self.dv
+        memory, maxima = view
+        proj = self.scratch(step, "proj", (N, self.w_all.shape[0]), torch.float32)
+        linear(u, self.w_all, proj)
+        g0 = 2 * qk + 2 * vv
+        log_a = self.scratch(step, "log_a", (N, nh), torch.float32)
+        b = self.scratch(step, "b", (N, nh), torch.float32)
+        m_tok = self.scratch(step, "m", (N, nh), torch.float32)
+        K.memory_gates(proj[:, g0:g0 + nh], proj[:, g0 + nh:g0 + 2 * nh], self.b_i, self.b_f, self.cap, maxima.state,
+                       step.slots, step.cu, log_a, b, m_tok, step.n_seqs, nh)
+        o = self.scratch(step, "o", (N, vv), torch.float32)
+        K.scalar_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], log_a, b, memory.state, step.slots,
+                      step.cu, o, step.n_seqs, nh, self.dk, self.dv, m_tok=m_tok, q_scale=self.dk ** -0.5)
+        y = self.scratch(step, "mix", (N, vv), step.dtype)
+        K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.dv, self.eps, K.GATE_SIGMOID, y)
+        linear(y, self.w_o, resid, accumulate=accumulate)
+
+
+@register("mixer", "parallel")
+class ParallelMixers(Part):
+    """Two mixers side by side that read the same input; the result is left_scale * left + right_scale * right.
+    Each keeps its own cache or state.  A block that can take the two results apart (``forward_sum``) adds them
+    inside its next kernel; ``forward`` adds them itself."""
+
+    nested_roles = {"left": "mixer", "right": "mixer"}
+    overwrites = True
+
+    def __init__(self, left, right, left_scale: float = 1.0, right_scale: float = 1.0):
+        self.left, self.right = left, right
+        self.left_scale, self.right_scale = float(left_scale), float(right_scale)
+        for side in (left, right):
+            if not getattr(side, "overwrites", False):
+                raise ValueError(f"mixer {getattr(side, 'kind', '?')} cannot write its result apart from the residual stream")
+
+    def nested(self):
+        return {"left": self.left, "right": self.right}
+
+    @property
+    def graph_safe(self):
+        return getattr(self.left, "graph_safe", True) and getattr(self.right, "graph_safe", True)
+
+    def cache_need(self):
+        self._split = []
+        needs = []
+        for side in (self.left, self.right):
+            need = side.cache_need()
+            many = isinstance(need, (list, tuple))
+            mine = list(need) if many else ([] if need is None else [need])
+            self._split.append((len(mine), many))
+            needs += mine
+        return needs
+
+    def _views(self, view):
+        if not hasattr(self, "_split"):
+            self.cache_need()
+        views, out, at = list(view), [], 0
+        for n, many in self._split:
+            out.append(views[at:at + n] if many else (views[at] if n else None))
+            at += n
+        return out
+
+    def forward_sum(self, u, step, view):
+        """[(result, scale), (result, scale)]: the two mixers' results in buffers of their own (float32)."""
+        N = u.shape[0]
+        lv, rv = self._views(view)
+        yl = self.scratch(step, "left", (N, self.left.hidden), torch.float32)
+        yr = self.scratch(step, "right", (N, self.right.hidden), torch.float32)
+        with profile_stage("mixer " + getattr(self.left, "kind", "?")):
+            self.left.forward(u, yl, step, lv, accumulate=False)
+        with profile_stage("mixer " + getattr(self.right, "kind", "?")):
+            self.right.forward(u, yr, step, rv, accumulate=False)
+        return [(yl, self.left_scale), (yr, self.right_scale)]
+
+    def forward(self, u, resid, step, view, accumulate: bool = True) -> None:
+        (yl, sl), (yr, sr) = self.forward_sum(u, step, view)
+        if accumulate:
+            resid.add_(yl, alpha=sl).add_(yr, alpha=sr)
+        else:
+            torch.add(yl * sl, yr, alpha=sr, out=resid)
