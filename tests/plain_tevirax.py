@@ -218,8 +218,10 @@ def route(h, w_router, r: dict):
     return pick, chosen / (chosen.sum(-1, keepdim=True) + 1e-20)
 
 
-def mixture(h, w, pre, mlp: dict, rnd=same, h_router=None):
+def mixture(h, w, pre, mlp: dict, rnd=same, h_router=None, router_inputs=None):
     T = h.shape[0]
+    if router_inputs is not None:
+        router_inputs.append(h)
     pick, weight = route(h if h_router is None else h_router, w[pre + "router"], mlp["router"])
     out = torch.zeros(T, w[pre + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(T):
@@ -239,8 +241,8 @@ def mixer(h, w, pre, c, eps, rnd=same):
     raise ValueError(c["type"])
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=F64, rnd=same, layers_out=None):
-    """Logits [T, vocab] of one whole sequence."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=F64, rnd=same, layers_out=None, router_inputs=None):
+    """Logits [T, vocab] of one whole sequence.  ``router_inputs`` (a list) gets the input of every mixture layer."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(cfg["norm"]["eps"])
     tok = torch.tensor(tokens, dtype=torch.long)
@@ -251,10 +253,21 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=F64,
         x = x + rms_norm(mixer(rnd(x), w, pre + "mix.", c, eps, rnd), w[pre + "norm1"], eps)
         if c.get("mlp"):
             h = rnd(x)
-            y = gated_mlp(h, w, pre + "mlp.", rnd) if c["mlp"]["kind"] == "dense" else mixture(h, w, pre + "mlp.", c["mlp"], rnd)
+            y = gated_mlp(h, w, pre + "mlp.", rnd) if c["mlp"]["kind"] == "dense" else \
+                mixture(h, w, pre + "mlp.", c["mlp"], rnd, router_inputs=router_inputs)
             x = x + rms_norm(y, w[pre + "norm2"], eps)
         if layers_out is not None:
             layers_out.append(x.clone())
     logits = rnd(rms_norm(x, w["final.norm"], eps)) @ w["head"].T
     cap = cfg.get("logit_softcap")
     return float(cap) * torch.tanh(logits / float(cap)) if cap else logits
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n_new: int, dtype=F64) -> List[int]:
+    """The n_new most likely next tokens, one after another, each from a whole forward pass."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        t = int(forward(cfg, w, toks, dtype)[-1].argmax())
+        toks.append(t)
+        out.append(t)
+    return out
