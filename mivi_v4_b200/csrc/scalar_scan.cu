@@ -200,3 +200,284 @@ MV_API int mv_memory_gates(const float* zi, int ld_i, const float* zf, int ld_f,
               b_out, m_tok, n_heads);
     return mv_launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same recurrence for steps that bring many tokens a sequence, in chunks of SC_CHUNK tokens.  With c_t the
+// sum of log a over the chunk's tokens up to t (all of it <= 0) and S0 the state before the chunk,
+//
+//     o_t   = e^(c_t) q_t^T S0 + sum_{s <= t} (q_t . k_s) e^(c_t - c_s) b_s v_s  (+ skip v_t),
+//     S_end = e^(c_last) S0 + sum_s e^(c_last - c_s) b_s k_s v_s^T.
+//
+// Every exponent is a difference of cumulative logarithms taken the right way round, so every factor lies in
+// (0, 1] (times b): nothing overflows however small a decay is.  Because the decay is one number a head, q and k
+// need no decayed copies: the products q_t . k_s are worked out once per GROUP of heads that share q and k (the
+// first kernel), and each head puts its own factors on them.  The second kernel walks a sequence's chunks with
+// the state in registers: a block is 16 value columns of one head of one sequence, its 32 half-warps each hold
+// RH key channels of every column.  With a normalizer the state's last column is fed ones instead of values and
+// comes out as n . q; a third kernel divides.  All of it is float32 on the CUDA cores.
+//
+// Chunks are numbered floor(cu[b] / SC_CHUNK) + b + c for chunk c of the step's sequence b: distinct numbers
+// below N / SC_CHUNK + n_seqs + 1 that need nothing from the host.
+#define SC_CHUNK 32
+#define SC_COLS 16
+#define SC_THREADS 256
+#define SC_SCAN_THREADS 512
+#define SC_GROUPS (SC_SCAN_THREADS / 16)
+#define SC_RED_STRIDE (SC_CHUNK * SC_COLS + 16)
+
+__global__ void __launch_bounds__(SC_THREADS)
+scalar_chunk_products_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                             const int* __restrict__ cu, float* __restrict__ G, int n_groups, int dk) {
+    mv_pdl_begin();
+    extern __shared__ float smem[];
+    const int lds = dk + 1;                         // odd row stride: rows of different tokens fall into different banks
+    float* qa = smem;                               // [SC_CHUNK][lds]
+    float* ka = qa + SC_CHUNK * lds;
+    const int c = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+    const int row0 = cu[b], len = cu[b + 1] - row0;
+    if (c * SC_CHUNK >= len) return;
+    const int nt = min(SC_CHUNK, len - c * SC_CHUNK);
+    const int first = row0 + c * SC_CHUNK;
+    const int chunk = row0 / SC_CHUNK + b + c;
+    for (int idx = threadIdx.x; idx < nt * dk; idx += SC_THREADS) {
+        const int t = idx / dk, i = idx - t * dk;
+        qa[t * lds + i] = q[(size_t)(first + t) * ldq + (size_t)g * dk + i];
+        ka[t * lds + i] = k[(size_t)(first + t) * ldk + (size_t)g * dk + i];
+    }
+    __syncthreads();
+    float* Gc = G + ((size_t)chunk * n_groups + g) * SC_CHUNK * SC_CHUNK;
+    for (int p = threadIdx.x; p < SC_CHUNK * SC_CHUNK; p += SC_THREADS) {
+        const int t = p / SC_CHUNK, s = p - t * SC_CHUNK;
+        float sum = 0.f;
+        if (s <= t && t < nt) {
+            const float* qt = qa + t * lds;
+            const float* kt = ka + s * lds;
+            for (int i = 0; i < dk; ++i) sum = fmaf(qt[i], kt[i], sum);
+        }
+        Gc[p] = sum;
+    }
+}
+
+template <int RH>
+__global__ void __launch_bounds__(SC_SCAN_THREADS)
+scalar_chunk_scan_kernel(const float* __restrict__ q, int ldq, const float* __restrict__ k, int ldk,
+                         const float* __restrict__ v, int ldv, const float* __restrict__ log_a, int ld_a,
+                         const float* __restrict__ b_in, int ld_b, const float* __restrict__ skip, float q_scale,
+                         const float* __restrict__ G, float* __restrict__ state, const int* __restrict__ slots,
+                         const int* __restrict__ cu, float* __restrict__ o, int n_heads, int heads_per_group, int dk,
+                         int dv, int ones_col) {
+    mv_pdl_begin();
+    constexpr int DKP = SC_GROUPS * RH;
+    extern __shared__ __align__(16) float smem[];
+    float* qt = smem;                               // [SC_CHUNK][DKP], zero beyond dk
+    float* kt = qt + SC_CHUNK * DKP;
+    float* vt = kt + SC_CHUNK * DKP;                // [SC_CHUNK][SC_COLS]
+    float* pt = vt + SC_CHUNK * SC_COLS;            // [SC_CHUNK][SC_CHUNK]
+    float* la = pt + SC_CHUNK * SC_CHUNK;           // [SC_CHUNK] log decays, then their running sum
+    float* bs = la + SC_CHUNK;                      // [SC_CHUNK] input factors
+    float* e1 = bs + SC_CHUNK;                      // [SC_CHUNK] e^(c_t) q_scale
+    float* e2 = e1 + SC_CHUNK;                      // [SC_CHUNK] e^(c_last - c_t) b_t
+    float* el = e2 + SC_CHUNK;                      // [1] e^(c_last) (padded to 16 floats)
+    float* red = el + 16;                           // [SC_GROUPS][SC_RED_STRIDE]: [SC_CHUNK][SC_COLS] a group
+    const int tile = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, col = tid & 15, grp = tid >> 4;
+    const int cols = dv + (ones_col >= 0 ? 1 : 0);  // the state's and the output's columns
+    const int j = tile * SC_COLS + col;
+    const int row0 = cu[b], len = cu[b + 1] - row0;
+    if (len <= 0) return;
+    const int slot = mv_read_slot(slots[b]);
+    const int n_groups = n_heads / heads_per_group, g = h / heads_per_group;
+    const size_t goff = (size_t)g * dk;
+    float* srow = state + (((size_t)slot * n_heads + h) * cols + (j < cols ? j : 0)) * dk;
+    float S[RH];
+#pragma unroll
+    for (int r = 0; r < RH; ++r) {
+        const int i = grp * RH + r;
+        S[r] = (j < cols && i < dk) ? srow[i] : 0.f;
+    }
+    const float sk = skip ? skip[h] : 0.f;
+    const int n_chunks = (len + SC_CHUNK - 1) / SC_CHUNK;
+    constexpr int IT = SC_CHUNK * DKP / SC_SCAN_THREADS;
+    static_assert(SC_CHUNK * SC_COLS == SC_SCAN_THREADS && SC_CHUNK * SC_CHUNK % SC_SCAN_THREADS == 0,
+                  "a thread requests one value of v and whole rounds of the products");
+    float rq[IT], rk[IT], rv, rp[SC_CHUNK * SC_CHUNK / SC_SCAN_THREADS], rla = 0.f, rb = 0.f;
+    auto request = [&](int c) {
+        const int nt = min(SC_CHUNK, len - c * SC_CHUNK);
+        const int first = row0 + c * SC_CHUNK;
+        const int chunk = row0 / SC_CHUNK + b + c;
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            const int idx = tid + it * SC_SCAN_THREADS, t = idx / DKP, i = idx - t * DKP;
+            const bool in = t < nt && i < dk;
+            rq[it] = in ? q[(size_t)(first + t) * ldq + goff + i] : 0.f;
+            rk[it] = in ? k[(size_t)(first + t) * ldk + goff + i] : 0.f;
+        }
+        {
+            const int t = tid / SC_COLS, cc = tile * SC_COLS + (tid - t * SC_COLS);
+            rv = t < nt ? (cc < dv ? v[(size_t)(first + t) * ldv + (size_t)h * dv + cc] : (cc == ones_col ? 1.f : 0.f)) : 0.f;
+        }
+        const float* Gc = G + ((size_t)chunk * n_groups + g) * SC_CHUNK * SC_CHUNK;
+#pragma unroll
+        for (int it = 0; it < SC_CHUNK * SC_CHUNK / SC_SCAN_THREADS; ++it) rp[it] = Gc[tid + it * SC_SCAN_THREADS];
+        if (tid < SC_CHUNK) {
+            rla = tid < nt ? log_a[(size_t)(first + tid) * ld_a + h] : 0.f;
+            rb = tid < nt ? b_in[(size_t)(first + tid) * ld_b + h] : 0.f;
+        }
+    };
+    request(0);
+    for (int c = 0; c < n_chunks; ++c) {
+        const int nt = min(SC_CHUNK, len - c * SC_CHUNK);
+        const int first = row0 + c * SC_CHUNK;
+        __syncthreads();                            // the chunk before is done with shared memory
+#pragma unroll
+        for (int it = 0; it < IT; ++it) {
+            qt[tid + it * SC_SCAN_THREADS] = rq[it];
+            kt[tid + it * SC_SCAN_THREADS] = rk[it];
+        }
+        vt[tid] = rv;
+#pragma unroll
+        for (int it = 0; it < SC_CHUNK * SC_CHUNK / SC_SCAN_THREADS; ++it) pt[tid + it * SC_SCAN_THREADS] = rp[it];
+        if (tid < SC_CHUNK) {
+            // the running sum of the log decays over the chunk (one warp), and the factors that follow from it
+            float run = rla;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const float up = __shfl_up_sync(0xffffffffu, run, d);
+                if (tid >= d) run += up;
+            }
+            const float last = __shfl_sync(0xffffffffu, run, nt - 1);
+            la[tid] = run;
+            bs[tid] = rb;
+            e1[tid] = expf(run) * q_scale;
+            e2[tid] = tid < nt ? expf(last - run) * rb : 0.f;
+            if (tid == 0) el[0] = expf(last);
+        }
+        __syncthreads();
+        if (c + 1 < n_chunks) request(c + 1);
+        // this head's factors on the group's products: e^(c_t - c_s) b_s q_scale (own entries only: no one else reads them yet)
+#pragma unroll
+        for (int it = 0; it < SC_CHUNK * SC_CHUNK / SC_SCAN_THREADS; ++it) {
+            const int p = tid + it * SC_SCAN_THREADS, t = p / SC_CHUNK, s = p - t * SC_CHUNK;
+            pt[p] = (s <= t && t < nt) ? pt[p] * expf(la[t] - la[s]) * bs[s] * q_scale : 0.f;
+        }
+        // what the chunk's tokens read from the state before the chunk: this half-warp's key channels
+#pragma unroll 4
+        for (int t = 0; t < SC_CHUNK; ++t) {
+            const float4* q4 = reinterpret_cast<const float4*>(qt + t * DKP + grp * RH);
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < RH; r += 4) {
+                const float4 x = q4[r >> 2];
+                acc = fmaf(x.x, S[r], acc); acc = fmaf(x.y, S[r + 1], acc);
+                acc = fmaf(x.z, S[r + 2], acc); acc = fmaf(x.w, S[r + 3], acc);
+            }
+            red[grp * SC_RED_STRIDE + t * SC_COLS + col] = acc;
+        }
+        // the state after the chunk
+        const float decay = el[0];
+#pragma unroll
+        for (int r = 0; r < RH; ++r) S[r] *= decay;
+#pragma unroll 4
+        for (int s = 0; s < SC_CHUNK; ++s) {
+            const float vj = vt[s * SC_COLS + col] * e2[s];
+            const float4* k4 = reinterpret_cast<const float4*>(kt + s * DKP + grp * RH);
+#pragma unroll
+            for (int r = 0; r < RH; r += 4) {
+                const float4 x = k4[r >> 2];
+                S[r] = fmaf(x.x, vj, S[r]); S[r + 1] = fmaf(x.y, vj, S[r + 1]);
+                S[r + 2] = fmaf(x.z, vj, S[r + 2]); S[r + 3] = fmaf(x.w, vj, S[r + 3]);
+            }
+        }
+        __syncthreads();
+        // outputs: the groups' shares in a fixed order, then the chunk's own tokens
+        for (int idx = tid; idx < nt * SC_COLS; idx += SC_SCAN_THREADS) {
+            const int t = idx / SC_COLS, cc = idx - t * SC_COLS;
+            float sum = 0.f;
+#pragma unroll
+            for (int gg = 0; gg < SC_GROUPS; ++gg) sum += red[gg * SC_RED_STRIDE + t * SC_COLS + cc];
+            sum *= e1[t];
+            for (int s = 0; s <= t; ++s) sum = fmaf(pt[t * SC_CHUNK + s], vt[s * SC_COLS + cc], sum);
+            const int oc = tile * SC_COLS + cc;
+            if (oc < dv) sum = fmaf(sk, vt[t * SC_COLS + cc], sum);
+            if (oc < cols) o[(size_t)(first + t) * n_heads * cols + (size_t)h * cols + oc] = sum;
+        }
+    }
+    if (j < cols && mv_slot_ok(slots[b])) {
+#pragma unroll
+        for (int r = 0; r < RH; ++r) {
+            const int i = grp * RH + r;
+            if (i < dk) srow[i] = S[r];
+        }
+    }
+}
+
+template <int RH>
+static int scalar_chunk_scan_launch(dim3 grid, cudaStream_t stream, const float* q, int ldq, const float* k, int ldk,
+                                    const float* v, int ldv, const float* log_a, int ld_a, const float* b, int ld_b,
+                                    const float* skip, float q_scale, const float* G, float* state, const int* slots,
+                                    const int* cu, float* o, int n_heads, int hpg, int dk, int dv, int ones_col) {
+    const size_t smem = sizeof(float) * ((size_t)2 * SC_CHUNK * SC_GROUPS * RH + SC_CHUNK * SC_COLS + SC_CHUNK * SC_CHUNK +
+                                         4 * SC_CHUNK + 16 + SC_GROUPS * SC_RED_STRIDE);
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(scalar_chunk_scan_kernel<RH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attr_set = true;
+    }
+    mv_launch(scalar_chunk_scan_kernel<RH>, grid, SC_SCAN_THREADS, smem, stream, q, ldq, k, ldk, v, ldv, log_a, ld_a, b, ld_b,
+              skip, q_scale, G, state, slots, cu, o, n_heads, hpg, dk, dv, ones_col);
+    return mv_launch_status();
+}
+
+// o[n, h, :] = o_aug[n, h, :dv] / (max(|o_aug[n, h, dv]|, e^(-m[n, h])) + 1e-6)
+__global__ void __launch_bounds__(256)
+memory_normalize_kernel(const float* __restrict__ o_aug, const float* __restrict__ m_tok, float* __restrict__ o,
+                        long long total, int dv) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const long long nh = idx / dv;
+    const int d = (int)(idx - nh * dv);
+    const float den = fmaxf(fabsf(o_aug[nh * (dv + 1) + dv]), expf(-m_tok[nh])) + 1e-6f;
+    o[idx] = o_aug[nh * (dv + 1) + d] / den;
+}
+
+// How many chunks the scratch of a step of N tokens in n_seqs sequences must hold.
+MV_API int mv_scalar_chunks(int N, int n_seqs) { return N / SC_CHUNK + n_seqs + 1; }
+
+// Arguments as mv_scalar_scan, plus the longest sequence's tokens (max_len) and scratch: G [chunks, groups,
+// SC_CHUNK, SC_CHUNK] with chunks = mv_scalar_chunks(N, n_seqs), and with a normalizer o_aug [N, n_heads * (dv + 1)].
+MV_API int mv_scalar_scan_chunked(const float* q, int ldq, const float* k, int ldk, const float* v, int ldv,
+                                  const float* log_a, int ld_a, const float* b, int ld_b, const float* skip,
+                                  const float* m_tok, float q_scale, float* state, const int* slots, const int* cu,
+                                  float* o, float* G, float* o_aug, int N, int n_seqs, int max_len, int n_heads,
+                                  int heads_per_group, int dk, int dv, int normalizer, cudaStream_t stream) {
+    if (n_seqs <= 0 || max_len <= 0) return 0;
+    if (dk < 1 || dk > 256 || dv < 1 || heads_per_group < 1 || n_heads % heads_per_group ||
+        (normalizer && (!m_tok || !o_aug)))
+        return (int)cudaErrorInvalidValue;
+    const int n_groups = n_heads / heads_per_group;
+    const size_t smem_a = sizeof(float) * (size_t)2 * SC_CHUNK * (dk + 1);
+    static size_t attr_a = 0;
+    if (smem_a > attr_a) {
+        cudaFuncSetAttribute(scalar_chunk_products_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_a);
+        attr_a = smem_a;
+    }
+    mv_launch(scalar_chunk_products_kernel, dim3((max_len + SC_CHUNK - 1) / SC_CHUNK, n_groups, n_seqs), SC_THREADS, smem_a,
+              stream, q, ldq, k, ldk, cu, G, n_groups, dk);
+    int code = mv_launch_status();
+    if (code) return code;
+    const int cols = dv + (normalizer ? 1 : 0);
+    const dim3 grid((cols + SC_COLS - 1) / SC_COLS, n_heads, n_seqs);
+    float* out = normalizer ? o_aug : o;
+    const int ones_col = normalizer ? dv : -1;
+    if (dk <= 128)
+        code = scalar_chunk_scan_launch<4>(grid, stream, q, ldq, k, ldk, v, ldv, log_a, ld_a, b, ld_b, skip, q_scale, G, state,
+                                           slots, cu, out, n_heads, heads_per_group, dk, dv, ones_col);
+    else
+        code = scalar_chunk_scan_launch<8>(grid, stream, q, ldq, k, ldk, v, ldv, log_a, ld_a, b, ld_b, skip, q_scale, G, state,
+                                           slots, cu, out, n_heads, heads_per_group, dk, dv, ones_col);
+    if (code || !normalizer) return code;
+    const long long total = (long long)N * n_heads * dv;
+    mv_launch(memory_normalize_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, (const float*)o_aug, m_tok, o, total, dv);
+    return mv_launch_status();
+}

@@ -66,6 +66,9 @@ _SIGNATURES = {
         "mv_rmsnorm_add_sum": [_P, _F, _P, _F, _P, _P, _P, _I, _I, _I, _F, _P],
         "mv_scalar_scan": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I,
                            _P],
+        "mv_scalar_chunks": [_I, _I],
+        "mv_scalar_scan_chunked": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _I,
+                                   _I, _I, _I, _I, _I, _P],
         "mv_memory_gates": [_P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
         "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
@@ -296,7 +299,7 @@ def _need(t: Optional[torch.Tensor], name: str, dtype=None, shape=None, optional
 
 _launches = 0
 # kernels launched by one call of each entry point
-_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2, "mv_causal_conv_silu": 2}
+_KERNELS_PER_CALL = {"mv_shortconv": 2, "mv_decay_scan_chunked": 2, "mv_causal_conv_silu": 2, "mv_scalar_scan_chunked": 2}
 
 
 def launch_count() -> int:
@@ -527,14 +530,17 @@ def rmsnorm_add_sum(y1: torch.Tensor, w: torch.Tensor, eps: float, resid: torch.
 def scalar_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_a: torch.Tensor, b: torch.Tensor,
                 state: torch.Tensor, slots: torch.Tensor, cu: torch.Tensor, out: torch.Tensor, n_seqs: int,
                 n_heads: int, dk: int, dv: int, *, heads_per_group: int = 1, skip: Optional[torch.Tensor] = None,
-                m_tok: Optional[torch.Tensor] = None, q_scale: float = 1.0) -> torch.Tensor:
+                m_tok: Optional[torch.Tensor] = None, q_scale: float = 1.0, max_len: int = 1, ws=None) -> torch.Tensor:
     """A matrix state per head with ONE decay per token and head: S <- a_t S + b_t k_t v_t^T, o_t = S^T q_t
     (+ skip_h v_t), over the step's tokens in order, from and into ``state`` [slots, heads, dv (+ 1), dk]
     (float32).  ``log_a`` and ``b`` [N, heads] are float32 (column slices are fine); q, k [N, groups * dk]
     with ``heads_per_group`` heads sharing a group's q and k; v [N, heads * dv].  With ``m_tok`` [N, heads] the
     state has one more value column, the normalizer n <- a_t n + b_t k_t, and
     o_t <- o_t / (max(|n . q_t|, exp(-m_tok)) + 1e-6).  Everything is computed in float32; the order of every
-    sum depends on dk alone, so any cut of a prompt gives the same numbers."""
+    sum depends on dk alone, so any cut of a prompt gives the same numbers.  ``max_len``: the most tokens that a
+    sequence brings; with ``ws`` (a Workspace, for scratch) steps of ``SCAN_CHUNKED_FROM`` tokens a sequence and
+    more take the kernels that walk a sequence in chunks of 32 tokens, whose sums come in another order (the
+    results differ from the token-by-token kernel's by rounding)."""
     N = out.shape[0]
     if not 1 <= dk <= MAX_SCAN_KEY_DIM:
         raise KernelError(f"scalar_scan: key size {dk} is outside 1..{MAX_SCAN_KEY_DIM}")
@@ -549,6 +555,22 @@ def scalar_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_a: torch.
     norm = m_tok is not None
     _need(state, "scalar_scan state", torch.float32, (None, n_heads, dv + (1 if norm else 0), dk))
     _guard("core", "scalar_scan", out.device, n_slots=state.shape[0])
+    if ws is not None and max_len >= SCAN_CHUNKED_FROM:
+        chunks = int(_fn("core", "mv_scalar_chunks")(N, int(n_seqs)))
+        G = ws.get("scalar_scan_products", (chunks, groups, SCAN_CHUNK, SCAN_CHUNK), torch.float32)
+        o_aug = ws.get("scalar_scan_o_aug", (N, n_heads * (dv + 1)), torch.float32) if norm else None
+        _check(_fn("core", "mv_scalar_scan_chunked")(
+            qp, ldq, kp, ldk, vp, ldv, ap, lda, bp, ldb, _need(skip, "scalar_scan skip", torch.float32, (n_heads,), True),
+            _need(m_tok, "scalar_scan m", torch.float32, (N, n_heads), True), float(q_scale), state.data_ptr(),
+            _need(slots, "slots", torch.int32), _need(cu, "cu", torch.int32),
+            _need(out, "scalar_scan out", torch.float32, (N, n_heads * dv)), G.data_ptr(),
+            o_aug.data_ptr() if norm else None, N, int(n_seqs), int(max_len), n_heads, int(heads_per_group), dk, dv,
+            int(norm), _stream()), "mv_scalar_scan_chunked")
+        add_launches(1 if norm else 0)
+        account(N * n_heads * (2 * dk // heads_per_group + 2 * dv) * 4 + 2 * n_seqs * n_heads * dk * dv * 4
+                + 2 * chunks * groups * SCAN_CHUNK * SCAN_CHUNK * 4,
+                4 * N * n_heads * dk * dv + N * n_heads * SCAN_CHUNK * dv + N * groups * SCAN_CHUNK * dk)
+        return out
     _check(_fn("core", "mv_scalar_scan")(
         qp, ldq, kp, ldk, vp, ldv, ap, lda, bp, ldb, _need(skip, "scalar_scan skip", torch.float32, (n_heads,), True),
         _need(m_tok, "scalar_scan m", torch.float32, (N, n_heads), True), float(q_scale), state.data_ptr(),

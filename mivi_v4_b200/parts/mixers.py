@@ -458,7 +458,7 @@ class Mamba2(Part):
         y = self.scratch(step, "y", (N, inner), torch.float32)
         K.scalar_scan(xbc[:, inner + gn:inner + 2 * gn], xbc[:, inner:inner + gn], xbc[:, :inner], log_a, b, ssm.state,
                       step.slots, step.cu, y, step.n_seqs, nh, self.state, self.dv, heads_per_group=nh // self.groups,
-                      skip=self.skip)
+                      skip=self.skip, max_len=step.max_len, ws=step.ws)
         g = self.scratch(step, "mix", (N, inner), step.dtype)
         K.gated_rmsnorm(y, proj[:, :inner], self.norm, inner // self.norm_groups, self.eps, K.GATE_SILU_FIRST, g)
         linear(g, self.w_o, resid, accumulate=accumulate)
@@ -513,7 +513,8 @@ class MatrixMemory(Part):
                        step.slots, step.cu, log_a, b, m_tok, step.n_seqs, nh)
         o = self.scratch(step, "o", (N, vv), torch.float32)
         K.scalar_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vv], log_a, b, memory.state, step.slots,
-                      step.cu, o, step.n_seqs, nh, self.dk, self.dv, m_tok=m_tok, q_scale=self.dk ** -0.5)
+                      step.cu, o, step.n_seqs, nh, self.dk, self.dv, m_tok=m_tok, q_scale=self.dk ** -0.5,
+                      max_len=step.max_len, ws=step.ws)
         y = self.scratch(step, "mix", (N, vv), step.dtype)
         K.gated_rmsnorm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.dv, self.eps, K.GATE_SIGMOID, y)
         linear(y, self.w_o, resid, accumulate=accumulate)

@@ -353,3 +353,73 @@ def test_scaled_embedding_with_positions_and_capped_logits():
     x = torch.tensor([[-100.0, -1.0, 0.0, 0.5, 40.0]])
     got = k.softcap_(x.to(DEV), 30.0)
     close(got, 30.0 * torch.tanh(x.double() / 30.0), 1e-6, "cap")
+
+
+# ------------------------------------------------------------------------------------------ recurrence in chunks
+def _workspace():
+    from mivi_v4_b200.engine.step import Workspace
+    return Workspace(DEV)
+
+
+@pytest.mark.parametrize("H,G,N,Pd", [(4, 2, 24, 16), (1, 1, 8, 3), (3, 3, 72, 20), (2, 1, 136, 33), (8, 1, 128, 64)])
+def test_chunked_scan_as_a_state_space_layer(H, G, N, Pd):
+    """Chunks full, one token short and one over; a decay that underflows within a chunk; steps that continue a
+    state; several sequences of unequal lengths in one step."""
+    k = K()
+    ws = _workspace()
+    g = torch.Generator().manual_seed(H * 7 + N)
+    for T, cuts in ((31, [31]), (32, [32]), (33, [33]), (97, [97]), (97, [40, 57]), (97, [16, 17, 64]), (80, [3, 77])):
+        x = torch.randn(T, H, Pd, generator=g, dtype=F64)
+        B, C = torch.randn(T, G, N, generator=g, dtype=F64), torch.randn(T, G, N, generator=g, dtype=F64)
+        dt = torch.rand(T, H, generator=g, dtype=F64) * 2 + 0.01
+        A, D = -torch.rand(H, generator=g, dtype=F64) * 2 - 0.01, torch.randn(H, generator=g, dtype=F64)
+        A[0] = -40.0                                     # e^(-40 dt): gone within a few tokens, e^(-1000) over a chunk
+        want = torch.cat([P.state_space_scan(x[:, a], B[:, a // (H // G)], C[:, a // (H // G)], dt[:, a], A[a], D[a]) for a in range(H)], -1)
+        wide = dev(torch.cat([x.reshape(T, -1), B.reshape(T, -1), C.reshape(T, -1)], -1))
+        inner, gn = H * Pd, G * N
+        log_a, b = dev(A[None, :] * dt), dev(dt)
+        state = torch.zeros(2, H, Pd, N, device=DEV)
+        outs, at = [], 0
+        for n in cuts:
+            rows = slice(at, at + n)
+            out = torch.full((n, inner), float("nan"), device=DEV)
+            k.scalar_scan(wide[rows, inner + gn:], wide[rows, inner:inner + gn], wide[rows, :inner], log_a[rows], b[rows],
+                          state, i32([1]), i32([0, n]), out, 1, H, N, Pd, heads_per_group=H // G, skip=dev(D), max_len=n, ws=ws)
+            outs.append(out)
+            at += n
+        close(torch.cat(outs), want, 3e-5, f"T {T} cuts {cuts}")
+        # the state the chunks leave is the state the token-by-token kernel leaves
+        ref = torch.zeros(2, H, Pd, N, device=DEV)
+        k.scalar_scan(wide[:, inner + gn:], wide[:, inner:inner + gn], wide[:, :inner], log_a, b, ref, i32([1]), i32([0, T]),
+                      torch.empty(T, inner, device=DEV), 1, H, N, Pd, heads_per_group=H // G, skip=dev(D))
+        close(state, ref.double().cpu(), 3e-5, "state")
+
+
+def test_chunked_scan_of_unequal_sequences_and_a_matrix_memory():
+    k = K()
+    ws = _workspace()
+    H, dk, dv, cap = 3, 40, 24, 9.0
+    g = torch.Generator().manual_seed(9)
+    lens = [70, 1, 33, 16]
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    q, kk = torch.randn(T, H, dk, generator=g, dtype=F64), torch.randn(T, H, dk, generator=g, dtype=F64)
+    v = torch.randn(T, H, dv, generator=g, dtype=F64)
+    zi, zf = 4 * torch.randn(T, H, generator=g, dtype=F64), 4 * torch.randn(T, H, generator=g, dtype=F64) + 2
+    zero = torch.zeros(H, dtype=F64)
+    i_log = cap * torch.tanh(zi / cap)
+    f_log = P.log_sigmoid(cap * torch.tanh(zf / cap))
+    want = torch.cat([torch.cat([P.matrix_memory_scan(q[a:b, h] * dk ** -0.5, kk[a:b, h], v[a:b, h], i_log[a:b, h], f_log[a:b, h])
+                                 for h in range(H)], -1) for a, b in zip(cu[:-1], cu[1:])])
+    memory, maxima = torch.zeros(5, H, dv + 1, dk, device=DEV), torch.zeros(5, H, device=DEV)
+    slots, cud = i32([4, 0, 2, 1]), i32(cu)
+    log_a, b, m = (torch.empty(T, H, device=DEV) for _ in range(3))
+    k.memory_gates(dev(zi), dev(zf), dev(zero), dev(zero), cap, maxima, slots, cud, log_a, b, m, len(lens), H)
+    out = torch.full((T, H * dv), float("nan"), device=DEV)
+    k.scalar_scan(dev(q.reshape(T, -1)), dev(kk.reshape(T, -1)), dev(v.reshape(T, -1)), log_a, b, memory, slots, cud, out,
+                  len(lens), H, dk, dv, m_tok=m, q_scale=dk ** -0.5, max_len=max(lens), ws=ws)
+    # the division by |n . q| amplifies float32 rounding where n . q nearly cancels, and the chunks sum in another order
+    close(out, want, 3e-4, "matrix memory in chunks")
+    assert memory[3].abs().max() == 0
