@@ -8,6 +8,7 @@ prefill, then generation timed without its first token).
     python bench.py --workload unequal32 | long32k      (the two further workloads, the same line for each)
     python bench.py --stages decode|prefill [--batch B] (where a step's time goes, by stage and kernel)
     python bench.py --design votavik [--stages ..]      (the Votavik decoder beside the LFM2 model of equal sizes)
+    python bench.py --design tevirax [--stages ..]      (the Tevirax decoder beside the Votavik decoder of equal sizes)
     python bench.py --kernel NAME [--m .. --n .. --k ..] (one kernel alone, for timing and for profilers)
 
 One "step" is one decode step of the whole batch.  Prints ONE JSON line:
@@ -211,6 +212,23 @@ def votavik_config(width, layers, heads, kv_heads, ff, vocab):
             "layers": [(gla, att, lig)[i % 3] for i in range(layers)]}
 
 
+def tevirax_config(width, layers, heads, kv_heads, ff, vocab):
+    """Two state space layers, then a layer of chunked attention beside a matrix memory, and so on; the first
+    layer's feed-forward is dense, the others are mixtures of 16 experts of an eighth of its width (4 chosen from
+    2 of 4 groups, and a shared one)."""
+    mamba = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
+    par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
+                    "rot": {"dims": 32, "base": 500000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
+           "right": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0},
+           "left_scale": 1.0, "right_scale": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 8},
+           "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    return {"architecture": "Tevirax", "vocab": vocab, "width": width, "max_positions": 4096, "norm": {"eps": 1e-6},
+            "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0,
+            "layers": [{"type": "parallel" if i % 3 == 2 else "mamba2", "mixer": par if i % 3 == 2 else mamba,
+                        "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe} for i in range(layers)]}
+
+
 def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
     cfg = dict(BENCH_CONFIG)
     cfg.update(hidden_size=width, num_hidden_layers=layers, num_attention_heads=heads, num_key_value_heads=kv_heads,
@@ -220,23 +238,26 @@ def lfm2_like(width, layers, heads, kv_heads, ff, vocab):
 
 
 def run_design(args, warmup: int) -> int:
-    """Prefill and decode throughput of the Votavik decoder at the sizes of DESIGN_SIZES, each beside the LFM2
-    model of equal sizes, random weights, bfloat16: one JSON line.  With --stages: where a step of the
-    w2048 Votavik model goes, kernel by kernel."""
+    """Prefill and decode throughput of a further design (--design) at the sizes of DESIGN_SIZES, each beside its
+    closest neighbour in the library at equal sizes (Votavik beside LFM2, Tevirax beside Votavik), random weights,
+    bfloat16: one JSON line.  With --stages: where a step of the design's model (--size) goes, kernel by kernel."""
     import torch
     from mivi_v4_b200 import measure, random_model
     pk, pk_src = peaks()
+    # the design that was asked for, beside its closest neighbour in the library at equal sizes
+    design_cfg = {"votavik": votavik_config, "tevirax": tevirax_config}[args.design]
+    beside, beside_cfg = {"votavik": ("lfm2", lfm2_like), "tevirax": ("votavik", votavik_config)}[args.design]
     if args.stages:
-        model = random_model(votavik_config(*DESIGN_SIZES["w2048"]), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
+        model = random_model(design_cfg(*DESIGN_SIZES[args.size]), seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
         lens = [args.tokens] if args.stages == "prefill" else [args.prompt_len] * args.batch
         rep = measure.stage_report(model, lens, prefill=args.stages == "prefill")
-        measure.print_stage_report(rep, f"{args.stages} step, {len(lens)} sequence(s) of {lens[0]} tokens, Votavik w2048", pk)
+        measure.print_stage_report(rep, f"{args.stages} step, {len(lens)} sequence(s) of {lens[0]} tokens, {args.design} {args.size}", pk)
         return 0
     steps = 32 if args.steps is None else args.steps
     rows = {}
     with ClockSampler() as clk:
         for name, sizes in DESIGN_SIZES.items():
-            for which, cfg in (("votavik", votavik_config(*sizes)), ("lfm2", lfm2_like(*sizes))):
+            for which, cfg in ((args.design, design_cfg(*sizes)), (beside, beside_cfg(*sizes))):
                 model = random_model(cfg, seed=0, dtype="bfloat16", device="cuda:0", on_device=True)
                 nums = measure.model_numbers(model)
                 row = {"weight_gb": nums["weight_bytes"] / 1e9}
@@ -253,7 +274,7 @@ def run_design(args, warmup: int) -> int:
                 rows[f"{name}/{which}"] = row
                 del model
                 torch.cuda.empty_cache()
-    print(json.dumps({"metric": "prefill and decode tokens/s of the Votavik decoder beside LFM2 at equal sizes, bf16, "
+    print(json.dumps({"metric": f"prefill and decode tokens/s of the {args.design} decoder beside {beside} at equal sizes, bf16, "
                                 "random weights", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
                       "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)", "peaks": pk_src,
                       "sizes": {k: dict(zip(("width", "layers", "heads", "kv_heads", "ff", "vocab"), v))
@@ -345,8 +366,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the further points and the end-to-end run")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
                     help="run one of the two further workloads instead of the default benchmark")
-    ap.add_argument("--design", default=None, choices=["votavik"],
-                    help="measure the Votavik decoder beside the LFM2 model of equal sizes instead of the default benchmark")
+    ap.add_argument("--size", default="w2048", choices=sorted(DESIGN_SIZES), help="with --design --stages: which size")
+    ap.add_argument("--design", default=None, choices=["votavik", "tevirax"],
+                    help="measure a further design beside its closest neighbour in the library at equal sizes (Votavik beside LFM2, "
+                         "Tevirax beside Votavik) instead of the default benchmark")
     ap.add_argument("--stages", default=None, choices=["decode", "prefill"],
                     help="print where the time of a decode step (of --batch sequences) or of the prefill goes")
     ap.add_argument("--prompt-len", type=int, default=PROMPT,

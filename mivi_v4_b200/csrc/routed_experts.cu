@@ -105,11 +105,13 @@ MV_API int mv_route(const float* z, int ld, float* dense, int* pick, float* pick
 // ------------------------------------------------------------------------------------------------
 // hid[n, c] = w[n, expert(c)] * silu(gate[n, c]) * up[n, c] over the columns of all experts laid end to end
 // (expert e owns [e * ff, (e + 1) * ff), a shared expert the `shared_ff` columns after them, with the weight of
-// column E).  gu [N, 2 * F]: all gates, then all ups.  Where the weight is zero nothing is computed.
+// column E).  gu [N, 2 * F] holds an expert's gates and ups together, [e * 2 ff, (e + 1) * 2 ff): alternating in
+// groups of 16 columns (16 gates, their 16 ups, ...) where `group` says so, else the gates, then the ups; the
+// shared expert's block follows with `shared_group`.  Where the weight is zero nothing is computed.
 template <typename TO>
 __global__ void __launch_bounds__(256)
 routed_glu_kernel(const float* __restrict__ gu, const float* __restrict__ dense, TO* __restrict__ hid, long long total,
-                  int F, int E, int ff, int cols) {
+                  int F, int E, int ff, int shared_ff, int cols, int group, int shared_group) {
     mv_pdl_begin();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
@@ -119,22 +121,155 @@ routed_glu_kernel(const float* __restrict__ gu, const float* __restrict__ dense,
     const float w = dense[n * cols + e];
     float out = 0.f;
     if (w != 0.f) {
-        const float g = gu[n * 2 * F + c], u = gu[n * 2 * F + F + c];
+        const int cc = c - e * ff, width = e < E ? ff : shared_ff, grp = e < E ? group : shared_group;
+        const float* blk = gu + n * 2 * F + (size_t)e * 2 * ff;
+        const int gi = grp ? (cc / grp) * 2 * grp + cc % grp : cc;
+        const float g = blk[gi], u = blk[gi + (grp ? grp : width)];
         out = w * (g / (1.0f + expf(-g))) * u;
     }
     hid[idx] = mv_from_f32<TO>(out);
 }
 
 MV_API int mv_routed_glu(const float* gu, const float* dense, void* hid, int hid_dtype, int N, int E, int ff,
-                         int shared_ff, cudaStream_t stream) {
+                         int shared_ff, int group, int shared_group, cudaStream_t stream) {
     if (N <= 0) return 0;
     const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0);
+    if ((group && ff % group) || (shared_group && shared_ff % shared_group)) return (int)cudaErrorInvalidValue;
     const long long total = (long long)N * F;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (hid_dtype == MV_DT_BF16)
         mv_launch(routed_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, gu, dense, (__nv_bfloat16*)hid, total, F, E,
-                  ff, cols);
+                  ff, shared_ff, cols, group, shared_group);
     else
-        mv_launch(routed_glu_kernel<float>, blocks, 256, 0, stream, gu, dense, (float*)hid, total, F, E, ff, cols);
+        mv_launch(routed_glu_kernel<float>, blocks, 256, 0, stream, gu, dense, (float*)hid, total, F, E, ff, shared_ff, cols,
+                  group, shared_group);
+    return mv_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// For steps of many tokens: the (token, choice) entries sorted by expert, so that every expert multiplies its own
+// tokens' rows only.  The sort is a stable counting sort: a block an expert walks the entries in order and ranks
+// its own; the ranks depend on the entries alone, not on which block ran first.
+__global__ void __launch_bounds__(256)
+expert_rank_kernel(const int* __restrict__ pick, int total, int* __restrict__ rank, int* __restrict__ counts) {
+    mv_pdl_begin();
+    __shared__ int warp_sum[8];
+    const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int base = 0;
+    for (int t0 = 0; t0 < total; t0 += 256) {
+        const int idx = t0 + tid;
+        const bool mine = idx < total && pick[idx] == e;
+        const unsigned votes = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) warp_sum[warp] = __popc(votes);
+        __syncthreads();
+        int before = 0, all = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+            before += w < warp ? warp_sum[w] : 0;
+            all += warp_sum[w];
+        }
+        if (mine) rank[idx] = base + before + __popc(votes & ((1u << lane) - 1u));
+        base += all;
+        __syncthreads();
+    }
+    if (tid == 0) counts[e] = base;
+}
+
+// place[entry] = (entries of the experts before its own) + its rank; the token's row is copied there.
+template <typename T>
+__global__ void __launch_bounds__(128)
+expert_gather_kernel(const int* __restrict__ pick, const int* __restrict__ rank, const int* __restrict__ counts,
+                     const T* __restrict__ x, int top, int H, int* __restrict__ place, T* __restrict__ xs) {
+    mv_pdl_begin();
+    __shared__ float scratch[33];
+    const int idx = blockIdx.x;
+    const int e = pick[idx];
+    int before = 0;
+    for (int i = threadIdx.x; i < e; i += blockDim.x) before += counts[i];
+    const int p = (int)(mv_block_sum((float)before, scratch) + 0.5f) + rank[idx];       // exact: counts are far below 2^24
+    if (threadIdx.x == 0) place[idx] = p;
+    const T* src = x + (size_t)(idx / top) * H;
+    T* dst = xs + (size_t)p * H;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) dst[h] = src[h];
+}
+
+// out[n, :] (+)= sum_k w[n, k] ys[place[n * top + k], :] + gate[n] shared[n, :], the choices in their order
+__global__ void __launch_bounds__(256)
+expert_combine_kernel(const float* __restrict__ ys, const int* __restrict__ place, const float* __restrict__ pick_w,
+                      const float* __restrict__ shared, const float* __restrict__ gate, int ld_gate,
+                      float* __restrict__ out, int top, int H, int accumulate) {
+    mv_pdl_begin();
+    const int n = blockIdx.x;
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k)
+            sum = fmaf(pick_w[(size_t)n * top + k], ys[(size_t)place[(size_t)n * top + k] * H + h], sum);
+        if (shared) sum = fmaf(gate ? gate[(size_t)n * ld_gate] : 1.f, shared[(size_t)n * H + h], sum);
+        float* o = out + (size_t)n * H + h;
+        *o = accumulate ? *o + sum : sum;
+    }
+}
+
+// pick [N, top] -> rank [N * top], counts [E]
+MV_API int mv_expert_rank(const int* pick, int total, int E, int* rank, int* counts, cudaStream_t stream) {
+    if (total <= 0 || E <= 0) return 0;
+    mv_launch(expert_rank_kernel, E, 256, 0, stream, pick, total, rank, counts);
+    return mv_launch_status();
+}
+
+// x [N, H] in `dtype` -> xs [N * top, H] sorted by expert; place [N * top] says where each entry went
+MV_API int mv_expert_gather(const int* pick, const int* rank, const int* counts, const void* x, int dtype, int N, int top,
+                            int H, int* place, void* xs, cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (dtype == MV_DT_BF16)
+        mv_launch(expert_gather_kernel<__nv_bfloat16>, N * top, 128, 0, stream, pick, rank, counts, (const __nv_bfloat16*)x,
+                  top, H, place, (__nv_bfloat16*)xs);
+    else
+        mv_launch(expert_gather_kernel<float>, N * top, 128, 0, stream, pick, rank, counts, (const float*)x, top, H, place,
+                  (float*)xs);
+    return mv_launch_status();
+}
+
+MV_API int mv_expert_combine(const float* ys, const int* place, const float* pick_w, const float* shared,
+                             const float* gate, int ld_gate, float* out, int N, int top, int H, int accumulate,
+                             cudaStream_t stream) {
+    if (N <= 0) return 0;
+    mv_launch(expert_combine_kernel, N, 256, 0, stream, ys, place, pick_w, shared, gate, ld_gate, out, top, H, accumulate);
+    return mv_launch_status();
+}
+
+// h[n, c] *= w[n, expert(c)] in place, for activations that a product's epilogue has already gated: eight
+// columns a thread (ff and shared_ff are multiples of 8 then), or one.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+scale_expert_columns_kernel(T* __restrict__ h, const float* __restrict__ dense, long long total, int F, int E, int ff,
+                            int cols) {
+    mv_pdl_begin();
+    const long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (idx >= total) return;
+    const long long n = idx / F;
+    const int c = (int)(idx - n * F);
+    const float w = dense[n * cols + (c < E * ff ? c / ff : E)];
+    if (V == 8) {
+        float x[8];
+        mv_load8(h + idx, x);
+        mv_store4(h + idx, x[0] * w, x[1] * w, x[2] * w, x[3] * w);
+        mv_store4(h + idx + 4, x[4] * w, x[5] * w, x[6] * w, x[7] * w);
+    } else {
+        h[idx] = mv_from_f32<T>(mv_to_f32(h[idx]) * w);
+    }
+}
+
+MV_API int mv_scale_expert_columns(void* h, int dtype, const float* dense, int N, int E, int ff, int shared_ff,
+                                   cudaStream_t stream) {
+    if (N <= 0) return 0;
+    const int F = E * ff + shared_ff, cols = E + (shared_ff ? 1 : 0);
+    const long long total = (long long)N * F;
+    const bool wide = ff % 8 == 0 && shared_ff % 8 == 0 && ((uintptr_t)h % 16) == 0;
+    const unsigned blocks = (unsigned)((total / (wide ? 8 : 1) + 255) / 256);
+#define SE_LAUNCH(T, V) mv_launch(scale_expert_columns_kernel<T, V>, blocks, 256, 0, stream, (T*)h, dense, total, F, E, ff, cols)
+    if (dtype == MV_DT_BF16) { if (wide) SE_LAUNCH(__nv_bfloat16, 8); else SE_LAUNCH(__nv_bfloat16, 1); }
+    else { if (wide) SE_LAUNCH(float, 8); else SE_LAUNCH(float, 1); }
+#undef SE_LAUNCH
     return mv_launch_status();
 }

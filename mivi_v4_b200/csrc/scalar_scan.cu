@@ -146,47 +146,54 @@ MV_API int mv_scalar_scan(const float* q, int ldq, const float* k, int ldk, cons
 //     i_t = cap tanh((zi_t + bi) / cap),  f_t = log sigmoid(cap tanh((zf_t + bf) / cap)),
 //     m_t = max(f_t + m_(t-1), i_t)   (m before a sequence's first token is 0: a zeroed state),
 //     log a_t = f_t + m_(t-1) - m_t,  b_t = e^(i_t - m_t).
-// A block is one sequence: all threads work out the gates of its tokens, one thread a head then walks the
-// maximum (the only part that is sequential), all threads finish b.  m is kept per slot and head.
+// The step m -> max(m + f, i) composes: first (f1, i1), then (f2, i2) is m -> max(m + f1 + f2, max(i1 + f2, i2)).
+// A warp is one (sequence, head): it takes 32 tokens at a time, a lane a token, scans the pairs with that rule
+// (five shuffles) and hands the last maximum on to the next 32.  A step of one token a sequence is the rule itself.
+// m is kept per slot and head.
 __device__ __forceinline__ float ss_log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 memory_gates_kernel(const float* __restrict__ zi, int ld_i, const float* __restrict__ zf, int ld_f,
                     const float* __restrict__ bi, const float* __restrict__ bf, float cap, float* __restrict__ m_state,
                     const int* __restrict__ slots, const int* __restrict__ cu, float* __restrict__ log_a,
-                    float* __restrict__ b_out, float* __restrict__ m_tok, int n_heads) {
+                    float* __restrict__ b_out, float* __restrict__ m_tok, int n_seqs, int n_heads) {
     mv_pdl_begin();
-    const int b = blockIdx.x;
+    const int warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (warp >= n_seqs * n_heads) return;
+    const int b = warp / n_heads, h = warp - b * n_heads;
     const int row0 = cu[b], len = cu[b + 1] - row0;
     if (len <= 0) return;
     const float inv_cap = 1.0f / cap;
-    for (int idx = threadIdx.x; idx < len * n_heads; idx += blockDim.x) {
-        const int t = idx / n_heads, h = idx - t * n_heads;
-        const size_t row = (size_t)(row0 + t);
-        const float il = cap * tanhf((zi[row * ld_i + h] + bi[h]) * inv_cap);
-        const float fl = ss_log_sigmoid(cap * tanhf((zf[row * ld_f + h] + bf[h]) * inv_cap));
-        b_out[row * n_heads + h] = il;
-        log_a[row * n_heads + h] = fl;
-    }
-    __syncthreads();
     const int slot = mv_read_slot(slots[b]);
-    for (int h = threadIdx.x; h < n_heads; h += blockDim.x) {
-        float m = m_state[(size_t)slot * n_heads + h];
-        for (int t = 0; t < len; ++t) {
-            const size_t at = (size_t)(row0 + t) * n_heads + h;
-            const float fl = log_a[at], il = b_out[at];
-            const float m_new = fmaxf(fl + m, il);
-            log_a[at] = fl + m - m_new;
-            m_tok[at] = m_new;
-            m = m_new;
+    float m = m_state[(size_t)slot * n_heads + h];
+    const float bih = bi[h], bfh = bf[h];
+    for (int t0 = 0; t0 < len; t0 += 32) {
+        const int t = t0 + lane;
+        const bool in = t < len;
+        const size_t row = (size_t)(row0 + (in ? t : 0));
+        const float il = in ? cap * tanhf((zi[row * ld_i + h] + bih) * inv_cap) : -INFINITY;
+        const float fl = in ? ss_log_sigmoid(cap * tanhf((zf[row * ld_f + h] + bfh) * inv_cap)) : 0.f;
+        float A = fl, B = il;                         // the tokens up to this lane's as one step m -> max(m + A, B)
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const float a_up = __shfl_up_sync(0xffffffffu, A, d), b_up = __shfl_up_sync(0xffffffffu, B, d);
+            if (lane >= d) {
+                B = fmaxf(b_up + A, B);
+                A = a_up + A;
+            }
         }
-        if (mv_slot_ok(slots[b])) m_state[(size_t)slot * n_heads + h] = m;
+        const float m_t = fmaxf(m + A, B);
+        float m_before = __shfl_up_sync(0xffffffffu, m_t, 1);
+        if (lane == 0) m_before = m;
+        if (in) {
+            const size_t at = row * n_heads + h;
+            log_a[at] = fl + m_before - m_t;
+            b_out[at] = expf(il - m_t);
+            m_tok[at] = m_t;
+        }
+        m = __shfl_sync(0xffffffffu, m_t, min(31, len - t0 - 1));
     }
-    __syncthreads();
-    for (int idx = threadIdx.x; idx < len * n_heads; idx += blockDim.x) {
-        const size_t at = (size_t)row0 * n_heads + idx;
-        b_out[at] = expf(b_out[at] - m_tok[at]);
-    }
+    if (lane == 0 && mv_slot_ok(slots[b])) m_state[(size_t)slot * n_heads + h] = m;
 }
 
 // zi, zf: the gates' projections [N, >= n_heads] with row strides; bi, bf [n_heads]; m_state [slots][n_heads];
@@ -196,8 +203,9 @@ MV_API int mv_memory_gates(const float* zi, int ld_i, const float* zf, int ld_f,
                            float* m_tok, int n_seqs, int n_heads, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (!(cap > 0.f) || n_heads < 1) return (int)cudaErrorInvalidValue;
-    mv_launch(memory_gates_kernel, n_seqs, 256, 0, stream, zi, ld_i, zf, ld_f, bi, bf, cap, m_state, slots, cu, log_a,
-              b_out, m_tok, n_heads);
+    const int warps = n_seqs * n_heads;
+    mv_launch(memory_gates_kernel, (warps + 3) / 4, 128, 0, stream, zi, ld_i, zf, ld_f, bi, bf, cap, m_state, slots, cu, log_a,
+              b_out, m_tok, n_seqs, n_heads);
     return mv_launch_status();
 }
 

@@ -33,13 +33,26 @@ def model_numbers(model) -> dict:
                         for g in plan.groups if not isinstance(g.need, KVNeed))
 
     def matrices(part) -> int:
-        n = sum(math.prod(spec.shape) for spec in part.param_specs().values() if spec.role == "matrix")
+        """Matrix elements that one token is multiplied with (a part that uses only some of its matrices for a
+        token, a mixture of experts, says how many through ``active_matrix_elements``)."""
+        if hasattr(part, "active_matrix_elements"):
+            n = part.active_matrix_elements()
+        else:
+            n = sum(math.prod(spec.shape) for spec in part.param_specs().values() if spec.role == "matrix")
         return n + sum(matrices(sub) for sub in part.nested().values())
     per_token = sum(matrices(model.blocks[e.block]) for e in model.schedule)
     mixers = [getattr(model.blocks[e.block], "mixer", None) for e in model.schedule]
 
     def mixer_flops(m, T: int) -> int:
         """Operations of one mixer beside its projections over a prompt of T tokens."""
+        if hasattr(m, "left") and hasattr(m, "right"):                 # two mixers side by side
+            return mixer_flops(m.left, T) + mixer_flops(m.right, T)
+        if getattr(m, "chunk", 0):                                     # softmax attention inside chunks of positions
+            full, rest = divmod(T, m.chunk)
+            pairs = full * m.chunk * (m.chunk + 1) // 2 + rest * (rest + 1) // 2
+            return 2 * m.nh * (m.dk + m.dv) * pairs
+        if hasattr(m, "state") and hasattr(m, "inner"):                # a state space layer: update and read-out
+            return 5 * m.nh * m.state * m.dv * T
         if hasattr(m, "hd") and hasattr(m, "nh"):                      # softmax attention, every earlier key
             return 4 * m.nh * m.hd * T * (T + 1) // 2
         if hasattr(m, "window") and hasattr(m, "dk"):                 # softmax attention, a window and kept first tokens

@@ -73,7 +73,11 @@ _SIGNATURES = {
         "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
         "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-        "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _P],
+        "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+        "mv_scale_expert_columns": [_P, _I, _P, _I, _I, _I, _I, _P],
+        "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
+        "mv_expert_gather": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+        "mv_expert_combine": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
     "bf16": {
@@ -656,19 +660,70 @@ def route(z: torch.Tensor, dense: torch.Tensor, pick: torch.Tensor, pick_w: torc
     account(N * cols * 8)
 
 
-def routed_glu(gu: torch.Tensor, dense: torch.Tensor, hid: torch.Tensor, n_experts: int, ff: int, shared_ff: int) -> torch.Tensor:
+def routed_glu(gu: torch.Tensor, dense: torch.Tensor, hid: torch.Tensor, n_experts: int, ff: int, shared_ff: int,
+               group: int = 0, shared_group: int = 0) -> torch.Tensor:
     """hid[n, c] = weight(n, expert of column c) * silu(gate[n, c]) * up[n, c] over the columns of all experts end to
-    end (then a shared expert's), from ``gu`` [N, 2 * F] float32 (all gates, then all ups) and the router's
-    dense weights; nothing is computed where the weight is zero."""
+    end (then a shared expert's), from ``gu`` [N, 2 * F] float32 and the router's dense weights; nothing is computed
+    where the weight is zero.  ``gu`` holds each expert's gates and ups together, [e * 2 ff, (e + 1) * 2 ff): the gates,
+    then the ups, or with ``group`` 16 alternating in groups of 16 columns; the shared expert's block likewise with
+    ``shared_group``."""
     N, F = hid.shape
     if F != n_experts * ff + shared_ff:
         raise KernelError(f"routed_glu: {F} columns for {n_experts} experts of {ff} and a shared one of {shared_ff}")
+    if (group and ff % group) or (shared_group and shared_ff % shared_group):
+        raise KernelError(f"routed_glu: widths {ff} and {shared_ff} against groups of {group} and {shared_group}")
     _check(_fn("core", "mv_routed_glu")(
         _need(gu, "routed_glu input", torch.float32, (N, 2 * F)),
         _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0))),
-        _need(hid, "routed_glu out"), _dt(hid), N, int(n_experts), int(ff), int(shared_ff), _stream()), "mv_routed_glu")
+        _need(hid, "routed_glu out"), _dt(hid), N, int(n_experts), int(ff), int(shared_ff), int(group), int(shared_group),
+        _stream()), "mv_routed_glu")
     account(N * F * (8 + hid.element_size()))
     return hid
+
+
+def scale_expert_columns(h: torch.Tensor, dense: torch.Tensor, n_experts: int, ff: int, shared_ff: int) -> torch.Tensor:
+    """h[n, c] *= weight(n, expert of column c) in place, over the columns of all experts end to end (then a shared
+    expert's): for activations that a product's epilogue has gated already."""
+    N, F = h.shape
+    if F != n_experts * ff + shared_ff:
+        raise KernelError(f"scale_expert_columns: {F} columns for {n_experts} experts of {ff} and a shared one of {shared_ff}")
+    _check(_fn("core", "mv_scale_expert_columns")(
+        _need(h, "gated activations"), _dt(h), _need(dense, "route weights", torch.float32, (N, n_experts + (1 if shared_ff else 0))),
+        N, int(n_experts), int(ff), int(shared_ff), _stream()), "mv_scale_expert_columns")
+    account(2 * N * F * h.element_size())
+    return h
+
+
+def expert_sort(pick: torch.Tensor, n_experts: int, x: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor,
+                place: torch.Tensor, xs: torch.Tensor) -> None:
+    """The (token, choice) entries of ``pick`` [N, top] sorted by expert (stable): ``counts`` [experts] entries an
+    expert, ``place`` [N * top] where each entry went, and the tokens' rows of ``x`` [N, H] copied to ``xs``
+    [N * top, H] in that order, so that an expert's rows lie together."""
+    N, top = pick.shape
+    H = x.shape[1]
+    _check(_fn("core", "mv_expert_rank")(
+        _need(pick, "picks", torch.int32), N * top, int(n_experts), _need(rank, "ranks", torch.int32, (N * top,)),
+        _need(counts, "counts", torch.int32, (n_experts,)), _stream()), "mv_expert_rank")
+    _check(_fn("core", "mv_expert_gather")(
+        pick.data_ptr(), rank.data_ptr(), counts.data_ptr(), _need(x, "expert_sort rows", None, (N, H)), _dt(x), N, top, H,
+        _need(place, "places", torch.int32, (N * top,)), _need(xs, "sorted rows", x.dtype, (N * top, H)), _stream()),
+        "mv_expert_gather")
+    account(N * (1 + top) * H * x.element_size())
+
+
+def expert_combine(ys: torch.Tensor, place: torch.Tensor, pick_w: torch.Tensor, shared: Optional[torch.Tensor],
+                   gate: Optional[torch.Tensor], out: torch.Tensor, accumulate: bool) -> torch.Tensor:
+    """out[n] (+)= sum_k pick_w[n, k] * ys[place[n * top + k]] (+ gate[n] * shared[n]), float32: the chosen experts'
+    results gathered back in the order of the choices.  ``gate`` [N, 1] may be a column of a wider matrix."""
+    N, H = out.shape
+    top = pick_w.shape[1]
+    gp, ldg = _cols(gate, "shared gate", N, 1) if gate is not None else (None, 0)
+    _check(_fn("core", "mv_expert_combine")(
+        _need(ys, "expert results", torch.float32, (N * top, H)), _need(place, "places", torch.int32, (N * top,)),
+        _need(pick_w, "pick weights", torch.float32, (N, top)), _need(shared, "shared result", torch.float32, (N, H), True),
+        gp, ldg, _need(out, "combine out", torch.float32), N, top, H, int(bool(accumulate)), _stream()), "mv_expert_combine")
+    account(N * H * 4 * (top + 2 + (1 if shared is not None else 0)))
+    return out
 
 
 MAX_SCAN_KEY_DIM = 256

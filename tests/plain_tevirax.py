@@ -195,8 +195,13 @@ def mamba2_mixer(h, w, pre, m, eps, rnd=same):
 
 
 # ---------------------------------------------------------------------------------- feed-forward
-def gated_mlp(h, w, pre, rnd=same):
-    return rnd(silu(h @ w[pre + "gate"].T) * (h @ w[pre + "up"].T)) @ w[pre + "down"].T
+def gated_mlp(h, w, pre, rnd=same, weight=None):
+    """``weight``: a factor on the gated activations (a router's weight): a narrow run may round them before the
+    factor and again after it, so both roundings are taken."""
+    act = rnd(silu(h @ w[pre + "gate"].T) * (h @ w[pre + "up"].T))
+    if weight is not None:
+        act = rnd(act * weight)
+    return act @ w[pre + "down"].T
 
 
 def route(h, w_router, r: dict):
@@ -226,9 +231,9 @@ def mixture(h, w, pre, mlp: dict, rnd=same, h_router=None, router_inputs=None):
     out = torch.zeros(T, w[pre + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(T):
         for e, a in zip(pick[t].tolist(), weight[t]):
-            out[t] += a * gated_mlp(h[t:t + 1], w, f"{pre}e{e}.", rnd)[0]
+            out[t] += gated_mlp(h[t:t + 1], w, f"{pre}e{e}.", rnd, weight=a)[0]
     if mlp.get("shared"):
-        out = out + torch.sigmoid(h @ w[pre + "shared.sg"].T) * gated_mlp(h, w, pre + "shared.", rnd)
+        out = out + gated_mlp(h, w, pre + "shared.", rnd, weight=torch.sigmoid(h @ w[pre + "shared.sg"].T))
     return out
 
 

@@ -220,3 +220,33 @@ def test_replay_program_whole_decoded_and_batched(dtype, tmp_path):
         got = torch.from_numpy(np.fromfile(path, dtype="<f4").reshape(-1, V).copy())
         want = torch.cat([plain(folder, reqs[k])[places] for k, places in exp])
         assert_rows(got, want, tdt, f"step {s['step']}", folder, [(reqs[k], places) for k, places in exp])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C", "D"])
+def test_long_steps_send_every_expert_its_own_tokens(name, dtype, tmp_path, monkeypatch):
+    """Steps that bring every expert many rows sort the (token, choice) entries by expert; with the bound lowered the
+    same path runs in steps of 8 tokens and more, against the plain logits."""
+    from mivi_v4_b200.parts.feed_forward import RoutedExperts
+    cfg, seed, folder = folder_for(tmp_path, name, dtype)
+    toks = prompts(cfg["vocab"], [290], seed + 3)[0]
+    want = plain(folder, toks)
+    eng = engine_for(folder, dtype)
+    s = eng.open()
+    assert_rows(eng.step([(s, toks)], "all"), want, dtype, f"{name} whole {len(toks)}", folder, toks)
+    eng.close(s)
+    monkeypatch.setattr(RoutedExperts, "SORTED_ROWS_AN_EXPERT", 1)
+    for piece in (8, 65, 290):
+        s = eng.open()
+        got = torch.cat([eng.step([(s, toks[i:i + piece])], "all") for i in range(0, len(toks), piece)])
+        eng.close(s)
+        assert_rows(got, want, dtype, f"{name} sorted experts, portions of {piece}", folder, toks)
+    reqs = prompts(cfg["vocab"], [40, 9, 75], seed + 4)
+    slots = [eng.open() for _ in reqs]
+    out = eng.step(list(zip(slots, reqs)), "all")
+    at = 0
+    for sl, r in zip(slots, reqs):
+        assert_rows(out[at:at + len(r)], plain(folder, r), dtype, f"{name} sorted experts, a batch", folder, r)
+        at += len(r)
+        eng.close(sl)
+    eng.cache.check()

@@ -214,12 +214,39 @@ def test_router_and_routed_activation(E, count, keep, top, shared):
     close(dense, want, 1e-6, "dense weights")
     assert ((dense[:, :E] != 0).sum(-1) == top).all()
     F = E * ff + sff
-    gu = torch.randn(N, 2 * F, generator=g, dtype=torch.float32)
+    gate, up = torch.randn(N, F, generator=g, dtype=torch.float32), torch.randn(N, F, generator=g, dtype=torch.float32)
+    # every expert's gates and ups together: the gates, then the ups
+    blocks = [torch.cat([gate[:, e * ff:(e + 1) * ff], up[:, e * ff:(e + 1) * ff]], 1) for e in range(E)]
+    if shared:
+        blocks.append(torch.cat([gate[:, E * ff:], up[:, E * ff:]], 1))
+    gu = torch.cat(blocks, 1)
     col_w = torch.cat([want[:, :E].repeat_interleave(ff, 1)] + ([want[:, E:].expand(N, sff)] if shared else []), 1)
     for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 4e-3)):
         hid = torch.full((N, F), float("nan"), dtype=dtype, device=DEV)
         k.routed_glu(dev(gu), dense, hid, E, ff, sff)
-        close(hid, col_w * P.silu(gu[:, :F].double()) * gu[:, F:].double(), tol, f"routed activation {dtype}")
+        close(hid, col_w * P.silu(gate.double()) * up.double(), tol, f"routed activation {dtype}")
+    # the entries sorted by expert, and the experts' results gathered back
+    H = 24
+    x = torch.randn(N, H, generator=g)
+    rank, place = (torch.empty(N * top, dtype=torch.int32, device=DEV) for _ in range(2))
+    counts = torch.empty(E, dtype=torch.int32, device=DEV)
+    xs = torch.full((N * top, H), float("nan"), device=DEV)
+    k.expert_sort(pick, E, dev(x), rank, counts, place, xs)
+    flat = pick.cpu().long().flatten()
+    assert counts.cpu().tolist() == torch.bincount(flat, minlength=E).tolist()
+    order = torch.argsort(flat, stable=True)
+    assert torch.equal(place.cpu().long()[order], torch.arange(N * top))
+    assert torch.equal(xs.cpu(), x[order // top])
+    ys = torch.randn(N * top, H, generator=g)
+    sh = torch.randn(N, H, generator=g) if shared else None
+    start = torch.randn(N, H, generator=g)
+    for accumulate in (False, True):
+        out = dev(start)
+        k.expert_combine(dev(ys), place, pw, None if sh is None else dev(sh), dense[:, E:E + 1] if shared else None, out, accumulate)
+        wantc = (pw.cpu().double()[:, :, None] * ys.double()[place.cpu().long()].view(N, top, H)).sum(1)
+        if shared:
+            wantc = wantc + want[:, E:E + 1] * sh.double()
+        close(out, wantc + (start.double() if accumulate else 0), 1e-5, "combine")
 
 
 # ------------------------------------------------------------------------------------------ attention

@@ -106,7 +106,7 @@ def route_direction(cfg, seed):
 def sharpen(weights, cfg, seed, router="random"):
     """Values of size one where the random-weights writer draws small ones.  ``router`` = "random" leaves the
     routers' rows as drawn.  "two_way": every router's rows are multiples of ONE direction u of the stream, so the
-    order of the scores depends on the sign of u . h only, and the position table carries ``ROUTE_PUSH`` u with a
+    order of the scores, and of the groups' sums of scores, depends on the sign of u . h only, and the position table carries ``ROUTE_PUSH`` u with a
     sign that changes every three positions: u . h stays far from zero, and a bfloat16 run (whose activations carry
     a relative noise of 2^-9) chooses the experts that the plain implementation chooses, while tokens still take
     one of two routes."""
@@ -135,8 +135,13 @@ def sharpen(weights, cfg, seed, router="random"):
             out[name] = (3.0 * w.float()).to(w.dtype)
         elif name.endswith(".router") and router == "two_way":
             E, W = w.shape
-            # unevenly spaced and not symmetric about zero: two groups' sums of scores tie at u . h = 0 only
-            factors = (4.0 * torch.linspace(0.0, 1.0, E) ** 1.5 - 1.5)[torch.randperm(E, generator=gen)]
+            # unevenly spaced factors, ascending, dealt to the groups in runs (every factor of one group above every
+            # factor of the next, so the groups' sums of scores keep their order whatever |u . h| is), then the groups
+            # and the experts inside a group shuffled
+            count = int((cfg["layers"][int(name.split(".")[0][1:])]["mlp"]["router"].get("groups") or {"count": 1})["count"])
+            factors = (4.0 * torch.linspace(0.0, 1.0, E) ** 1.5 - 1.5).view(count, E // count)
+            factors = factors[torch.randperm(count, generator=gen)]
+            factors = torch.stack([row[torch.randperm(E // count, generator=gen)] for row in factors]).flatten()
             out[name] = (factors[:, None] * (1.8 / ROUTE_PUSH) * u[None, :]).to(w.dtype)
     return out
 
