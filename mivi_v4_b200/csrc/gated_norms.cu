@@ -80,7 +80,7 @@ gated_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gate
 
 // The same with one block per (row, group), for groups of many values (a norm over all heads of a wide layer).
 template <typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_rmsnorm_block_kernel(const float* __restrict__ x, const float* __restrict__ gate, int ld_gate,
                            const float* __restrict__ w, int w_len, TO* __restrict__ y, int C, int group, float eps,
                            int act) {
@@ -113,11 +113,13 @@ MV_API int mv_gated_rmsnorm(const float* x, const float* gate, int ld_gate, cons
     if (group < 1 || C % group || w_len < 1) return (int)cudaErrorInvalidValue;
     const long long n_groups = (long long)N * (C / group);
     if (group >= 512) {
+        // few (row, group) pairs of many values each (a decode step of a wide layer): more threads a block
+        const int threads = (n_groups < 1024 && group >= 4096) ? 1024 : ((n_groups < 2048 && group >= 2048) ? 512 : 256);
         if (y_dtype == MV_DT_BF16)
-            mv_launch(gated_rmsnorm_block_kernel<__nv_bfloat16>, (unsigned)n_groups, 256, 0, stream, x, gate, ld_gate, w,
+            mv_launch(gated_rmsnorm_block_kernel<__nv_bfloat16>, (unsigned)n_groups, threads, 0, stream, x, gate, ld_gate, w,
                       w_len, (__nv_bfloat16*)y, C, group, eps, act);
         else
-            mv_launch(gated_rmsnorm_block_kernel<float>, (unsigned)n_groups, 256, 0, stream, x, gate, ld_gate, w, w_len,
+            mv_launch(gated_rmsnorm_block_kernel<float>, (unsigned)n_groups, threads, 0, stream, x, gate, ld_gate, w, w_len,
                       (float*)y, C, group, eps, act);
         return mv_launch_status();
     }

@@ -66,7 +66,54 @@ step_size_kernel(const float* __restrict__ raw, int ld, const float* __restrict_
     log_a[idx] = -expf(a_log[h]) * dt;
 }
 
+// A step of one token a sequence: the convolution's output, the kept inputs' shift and the step size in ONE
+// kernel.  A thread is a (sequence, channel): it alone reads and writes that channel's kept inputs, so nothing
+// races; the threads after the channels take the heads' step sizes.  Row b of the step is sequence b's token.
+__global__ void __launch_bounds__(256)
+ssm_decode_prepare_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
+                          const float* __restrict__ bias, float* __restrict__ state, const int* __restrict__ slots,
+                          float* __restrict__ out, int C, int K, const float* __restrict__ raw, int ld_raw,
+                          const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ log_a,
+                          float* __restrict__ b_out, int H) {
+    mv_pdl_begin();
+    const int b = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= C + H) return;
+    if (c >= C) {
+        const int h = c - C;
+        const float z = raw[(size_t)b * ld_raw + h] + dt_bias[h];
+        const float dt = z > 20.f ? z : log1pf(expf(z));
+        b_out[(size_t)b * H + h] = dt;
+        log_a[(size_t)b * H + h] = -expf(a_log[h]) * dt;
+        return;
+    }
+    const bool ok = mv_slot_ok(slots[b]);
+    float* st = state + (size_t)mv_read_slot(slots[b]) * (K - 1) * C;
+    const float x = u[(size_t)b * ld + c];
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = 0; j < K - 1; ++j) {
+        const float kept = st[(size_t)j * C + c];
+        acc = fmaf(taps[(size_t)c * K + j], kept, acc);
+        if (j > 0 && ok) st[(size_t)(j - 1) * C + c] = kept;
+    }
+    if (K > 1 && ok) st[(size_t)(K - 2) * C + c] = x;
+    acc = fmaf(taps[(size_t)c * K + K - 1], x, acc);
+    out[(size_t)b * C + c] = acc / (1.0f + expf(-acc));
+}
+
 MV_GUARD_SETTER(state_space)
+
+// One token a sequence (row b belongs to slots[b]): mv_causal_conv_silu and mv_step_size together.
+MV_API int mv_ssm_decode_prepare(const float* u, int ld, const float* taps, const float* bias, float* state,
+                                 const int* slots, float* out, int n_seqs, int C, int K, const float* raw, int ld_raw,
+                                 const float* dt_bias, const float* a_log, float* log_a, float* b_out, int H,
+                                 cudaStream_t stream) {
+    if (n_seqs <= 0) return 0;
+    if (K < 1 || K > SP_MAX_TAPS || C < 1 || H < 1) return (int)cudaErrorInvalidValue;
+    mv_launch(ssm_decode_prepare_kernel, dim3((C + H + 255) / 256, n_seqs), 256, 0, stream, u, ld, taps, bias, state, slots,
+              out, C, K, raw, ld_raw, dt_bias, a_log, log_a, b_out, H);
+    return mv_launch_status();
+}
 
 // u: the convolution's input columns [N, C] with row stride ld; taps [C, K]; bias [C] or null; state
 // [slots][K - 1][C]; out [N, C] dense.  Two kernels: the outputs (which read the kept inputs), then the kept

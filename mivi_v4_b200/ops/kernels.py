@@ -71,6 +71,7 @@ _SIGNATURES = {
                                    _I, _I, _I, _I, _I, _P],
         "mv_memory_gates": [_P, _I, _P, _I, _P, _P, _F, _P, _P, _P, _P, _P, _P, _I, _I, _P],
         "mv_causal_conv_silu": [_P, _I, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+        "mv_ssm_decode_prepare": [_P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _P, _P, _P, _I, _P],
         "mv_step_size": [_P, _I, _P, _P, _P, _P, _I, _I, _P],
         "mv_route": [_P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
         "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
@@ -633,6 +634,29 @@ def step_size(raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, log
         rp, ldr, _need(dt_bias, "dt bias", torch.float32, (H,)), _need(a_log, "A_log", torch.float32, (H,)),
         _need(log_a, "log_a", torch.float32), _need(b, "b", torch.float32, (N, H)), N, H, _stream()), "mv_step_size")
     account(N * H * 12)
+
+
+def ssm_decode_prepare(u: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                       slots: torch.Tensor, out: torch.Tensor, raw: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                       log_a: torch.Tensor, b: torch.Tensor) -> None:
+    """:func:`causal_conv_silu` and :func:`step_size` in one kernel for a step of one token a sequence (row i of
+    the step is the token of ``slots[i]``)."""
+    N, C = out.shape
+    K, H = taps.shape[1], log_a.shape[1]
+    if not 1 <= K <= MAX_CONV_K:
+        raise KernelError(f"ssm_decode_prepare: {K} taps are outside 1..{MAX_CONV_K}")
+    if slots.numel() != N:
+        raise KernelError(f"ssm_decode_prepare: {N} rows for {slots.numel()} sequences; this kernel takes one token a sequence")
+    up, ldu = _cols(u, "ssm_decode_prepare input", N, C)
+    rp, ldr = _cols(raw, "ssm_decode_prepare step sizes", N, H)
+    _guard("core", "state_space", out.device, n_slots=state.shape[0])
+    _check(_fn("core", "mv_ssm_decode_prepare")(
+        up, ldu, _need(taps, "conv taps", torch.float32, (C, K)), _need(bias, "conv bias", torch.float32, (C,), True),
+        _need(state, "conv state", torch.float32, (None, K - 1, C)) if K > 1 else None, _need(slots, "slots", torch.int32),
+        _need(out, "conv out", torch.float32), N, C, K, rp, ldr, _need(dt_bias, "dt bias", torch.float32, (H,)),
+        _need(a_log, "A_log", torch.float32, (H,)), _need(log_a, "log_a", torch.float32, (N, H)),
+        _need(b, "b", torch.float32, (N, H)), H, _stream()), "mv_ssm_decode_prepare")
+    account(N * (C * 8 + H * 12) + 2 * N * (K - 1) * C * 4, 2 * N * C * K)
 
 
 MAX_EXPERTS = 1024

@@ -450,11 +450,17 @@ class Mamba2(Part):
         proj = self.scratch(step, "proj", (N, self.w_in.shape[0]), torch.float32)
         linear(u, self.w_in, proj)
         xbc = self.scratch(step, "xbc", (N, self.channels), torch.float32)
-        K.causal_conv_silu(proj[:, inner:inner + self.channels], self.taps, self.b_conv, conv.state, step.seq_of, step.cu,
-                           step.slots, xbc, step.n_seqs)
         log_a = self.scratch(step, "log_a", (N, nh), torch.float32)
         b = self.scratch(step, "b", (N, nh), torch.float32)
-        K.step_size(proj[:, inner + self.channels:inner + self.channels + nh], self.dt_bias, self.a_log, log_a, b)
+        raw_dt = proj[:, inner + self.channels:inner + self.channels + nh]
+        if step.is_decode and N == step.n_seqs:
+            # one token a sequence: convolution, kept inputs and step size in one kernel
+            K.ssm_decode_prepare(proj[:, inner:inner + self.channels], self.taps, self.b_conv, conv.state, step.slots, xbc,
+                                 raw_dt, self.dt_bias, self.a_log, log_a, b)
+        else:
+            K.causal_conv_silu(proj[:, inner:inner + self.channels], self.taps, self.b_conv, conv.state, step.seq_of,
+                               step.cu, step.slots, xbc, step.n_seqs)
+            K.step_size(raw_dt, self.dt_bias, self.a_log, log_a, b)
         y = self.scratch(step, "y", (N, inner), torch.float32)
         K.scalar_scan(xbc[:, inner + gn:inner + 2 * gn], xbc[:, inner:inner + gn], xbc[:, :inner], log_a, b, ssm.state,
                       step.slots, step.cu, y, step.n_seqs, nh, self.state, self.dv, heads_per_group=nh // self.groups,

@@ -450,3 +450,28 @@ def test_chunked_scan_of_unequal_sequences_and_a_matrix_memory():
     # the division by |n . q| amplifies float32 rounding where n . q nearly cancels, and the chunks sum in another order
     close(out, want, 3e-4, "matrix memory in chunks")
     assert memory[3].abs().max() == 0
+
+
+@pytest.mark.parametrize("taps", [1, 2, 4])
+def test_one_token_a_sequence_convolution_and_step_size_in_one_kernel(taps):
+    k = K()
+    C, H, T, B = 21, 3, 9, 3
+    g = torch.Generator().manual_seed(taps + 40)
+    u = torch.randn(B, T, 2 + C + H, generator=g, dtype=F64)                 # [.. | channels | step sizes] a token
+    w, bias = torch.randn(C, taps, generator=g, dtype=F64), torch.randn(C, generator=g, dtype=F64)
+    dt_bias, a_log = torch.randn(H, generator=g, dtype=F64), torch.randn(H, generator=g, dtype=F64)
+    want = torch.stack([P.silu(P.causal_taps(u[b, :, 2:2 + C], w, bias)) for b in range(B)])
+    state = torch.zeros(4, max(taps - 1, 0), C, device=DEV)
+    slots = i32([2, 0, 3])
+    for t in range(T):
+        rows = dev(u[:, t])
+        out = torch.full((B, C), float("nan"), device=DEV)
+        log_a, b = torch.empty(B, H, device=DEV), torch.empty(B, H, device=DEV)
+        k.ssm_decode_prepare(rows[:, 2:2 + C], dev(w), dev(bias), state, slots, out, rows[:, 2 + C:], dev(dt_bias), dev(a_log), log_a, b)
+        close(out, want[:, t], 1e-5, f"taps {taps} token {t}")
+        dt = P.softplus(u[:, t, 2 + C:] + dt_bias)
+        close(b, dt, 1e-6, "dt")
+        close(log_a, -torch.exp(a_log) * dt, 1e-6, "log a")
+    if taps > 1:
+        assert state[1].abs().max() == 0
+        close(state[0], u[1, T - (taps - 1):, 2:2 + C], 1e-6, "kept inputs")
