@@ -1,7 +1,7 @@
 """Typed configuration of the Tevirax decoder, read from its config.json.
 
 The file names its architecture with one string, ``"architecture": "Tevirax"``, and gives the model's sizes
-(``vocab``, ``width``, ``max_positions``), the token embedding's factor (``embedding.scale``), the norm's eps
+(``vocab``, ``width``, ``max_positions``: the position table's rows, taken from the checkpoint where absent), the token embedding's factor (``embedding.scale``), the norm's eps
 (``norm.eps``), the cap on the logits (``logit_softcap``) and a list ``layers`` whose entries say which mixer the
 layer has (``type``: mamba2 | parallel), the mixer's sizes and constants (``mixer``) and the feed-forward
 (``mlp``: ``kind`` dense | moe, or null for none).  Every size and constant is taken from there; nothing is
@@ -113,7 +113,7 @@ class TeviraxConfig:
     width: int
     norm_eps: float
     embedding_scale: float
-    max_positions: int
+    max_positions: Optional[int]
     logit_softcap: float
     layers: List[TeviraxLayer] = field(default_factory=list)
     eos_token_id: Optional[int] = None
@@ -124,7 +124,8 @@ class TeviraxConfig:
         eps = _num("config key 'norm'", _obj("config", d, "norm"), "eps")
         emb = d.get("embedding")
         scale = _num("config key 'embedding'", emb, "scale") if isinstance(emb, dict) and emb.get("scale") is not None else 1.0
-        max_positions = _int("config", d, "max_positions")
+        # absent: the position table's length is the checkpoint's to say
+        max_positions = None if d.get("max_positions") is None else _int("config", d, "max_positions")
         cap = d.get("logit_softcap")
         cap = 0.0 if cap is None else _num("config", d, "logit_softcap", positive=True)
         raw = d.get("layers")

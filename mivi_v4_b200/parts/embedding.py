@@ -34,19 +34,19 @@ class Embedding(Part):
 @register("embedding", "table_scaled_positions")
 class ScaledEmbeddingWithPositions(Part):
     """x_t = E[token_t] * scale + P[position_t]: a scaled token embedding plus a learned position vector
-    (``max_positions`` None: no position table).  With ``hand_rounded`` the rows are also written in the model's
+    (``positions`` False: no position table; ``max_positions`` None: as many rows as the checkpoint has).  With ``hand_rounded`` the rows are also written in the model's
     dtype and handed to the first block through ``step.handed`` as ("stream", rows): a block whose first
     sublayer reads the stream itself then needs no rounding pass."""
 
     def __init__(self, vocab: int, hidden: int, scale: float = 1.0, max_positions: Optional[int] = None,
-                 hand_rounded: bool = False):
+                 hand_rounded: bool = False, positions: bool = True):
         self.vocab, self.hidden, self.scale = int(vocab), int(hidden), float(scale)
         self.max_positions = None if max_positions is None else int(max_positions)
-        self.hand_rounded = bool(hand_rounded)
+        self.hand_rounded, self.has_positions = bool(hand_rounded), bool(positions)
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         specs = {"weight": ParamSpec((self.vocab, self.hidden))}
-        if self.max_positions is not None:
+        if self.has_positions:
             specs["positions"] = ParamSpec((self.max_positions, self.hidden))
         return specs
 
@@ -61,6 +61,9 @@ class ScaledEmbeddingWithPositions(Part):
         rounded = None
         if self.hand_rounded and step.dtype != torch.float32:
             rounded = step.ws.get("stream_rounded", (N, self.hidden), step.dtype)
+        if self.positions is not None and step.max_context > self.positions.shape[0]:
+            raise K.KernelError(f"a sequence reaches position {step.max_context - 1}; the position table has "
+                                f"{self.positions.shape[0]} rows")
         K.embed_scaled_pos(self.weight, step.tokens, self.scale, self.positions, step.positions, x, rounded)
         step.handed = ("stream", rounded) if rounded is not None else None
         return x

@@ -118,6 +118,8 @@ def test_config_reader_and_name_table():
     assert names["l1.mix.in"].shape == (2 * 64 + 2 * 2 * 24 + 4, 64) and names["l1.mix.conv"].shape == (64 + 96, 4)
     assert "l2.norm2" not in names and "l2.mlp.gate" not in names and names["l3.mlp.gate"].shape == (40, 64)
     assert "l1.mlp.router" not in expected_tensors(TEV_B) and "l0.mlp.shared.sg" not in expected_tensors(TEV_B)
+    without = {k: v for k, v in TEV_A.items() if k != "max_positions"}       # the table's length is then the checkpoint's to say
+    assert expected_tensors(without)["pos"].shape == (None, 64)
 
     def broken(edit):
         c = json.loads(json.dumps(TEV_A))
@@ -130,7 +132,7 @@ def test_config_reader_and_name_table():
     broken(lambda c: c["layers"][0]["mlp"]["router"].update(top=9))
     broken(lambda c: c["layers"][1]["mixer"].update(groups=3))
     broken(lambda c: c["layers"][1]["mixer"].update(norm_groups=7))
-    broken(lambda c: c.pop("max_positions"))
+    broken(lambda c: c.update(max_positions=0))
     broken(lambda c: c["layers"][0]["mixer"]["right"].update(gate_cap=0))
 
 
