@@ -168,3 +168,17 @@ def test_two_way_routers_stay_far_from_a_close_call(tmp_path):
             x = h @ u
             assert x.abs().min() > 4.0, (name, float(x.abs().min()))
             assert (x > 0).any() and (x < 0).any()
+
+
+def test_command_line_writes_and_describes_a_model_folder(tmp_path, capsys):
+    from mivi_v4_b200.cli import main
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(TEV_A))
+    out = tmp_path / "model"
+    assert main(["random", "--config", str(cfg), "--seed", "1", "--out", str(out)]) == 0
+    assert (out / "config.json").is_file() and (out / "model.safetensors").is_file()
+    capsys.readouterr()
+    assert main(["info", "-m", str(out)]) == 0
+    text = capsys.readouterr().out
+    assert "architecture: Tevirax" in text and "logit_softcap: 20.0" in text
+    assert "l0.mix.left.q.norm" in text and "l0.mix.right.f.b" in text and "l0.mlp.e11.down" in text and "l1.mix.A_log" in text
