@@ -68,8 +68,19 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const float* __restrict__ bias, void* __restrict__ out, int mode, int M, int N, int K, int ldo,
-               const RowScale rs, int* __restrict__ err) {
+               const RowScale rs, int* __restrict__ err, const int* __restrict__ tile_group, int b_row_step,
+               int b_k_step) {
     using L = SmemLayout<BN, STAGES>;
+    // A grouped product (tile_group not null): the rows of X are sorted by group and padded so that no tile of 128
+    // rows holds two groups; tile_group says which group a tile belongs to (negative: a spare tile, nothing to do),
+    // and the group picks its part of W: b_row_step rows further down (W = the groups' matrices one below the
+    // other) or b_k_step columns further along K (W = the groups' matrices side by side).  N and K are one group's.
+    int group = 0;
+    if (tile_group) {
+        group = tile_group[blockIdx.y];
+        if (group < 0) return;                     // the whole block, before any barrier or tensor memory exists
+    }
+    const int b_row0 = group * b_row_step, b_k0 = group * b_k_step;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned long long* bars = (unsigned long long*)(smem + L::TILE_BYTES);
@@ -108,7 +119,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 mbar_expect_tx(full0 + 8 * s, L::STAGE_BYTES);
                 const unsigned a_dst = tiles0 + s * L::STAGE_BYTES;
                 tma_load_2d(a_dst, &map_a, kb * BK, m0, full0 + 8 * s);
-                tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK, n0, full0 + 8 * s);
+                tma_load_2d(a_dst + L::A_BYTES, &map_b, kb * BK + b_k0, n0 + b_row0, full0 + 8 * s);
             }
         }
     } else if (warp == 1) {
@@ -342,7 +353,25 @@ int launch(const void* X, const void* W, const float* bias, void* out, int mode,
         attr_set = true;
     }
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, rs, err);
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(ma, mb, bias, out, mode, M, N, K, ldo, rs, err, nullptr, 0, 0);
+    return mv_launch_status();
+}
+
+// The grouped form: X [M, K] sorted by group, W [w_rows, w_cols] holding every group's matrix.
+template <int BN, int STAGES>
+int launch_grouped(const void* X, const void* W, void* out, int mode, int M, int N, int K, int ldo, int w_rows, int w_cols,
+                   const int* tile_group, int b_row_step, int b_k_step, int* err, cudaStream_t stream) {
+    using L = SmemLayout<BN, STAGES>;
+    CUtensorMap ma, mb;
+    if (!tensor_map(X, M, K, BM, &ma) || !tensor_map(W, w_rows, w_cols, BN, &mb)) return (int)cudaErrorInvalidValue;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        attr_set = true;
+    }
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    gemm_tc_kernel<BN, STAGES><<<grid, THREADS, L::TOTAL, stream>>>(ma, mb, nullptr, out, mode, M, N, K, ldo, RowScale{}, err,
+                                                                   tile_group, b_row_step, b_k_step);
     return mv_launch_status();
 }
 
@@ -367,4 +396,21 @@ MV_API int mv_gemm_tc(const void* X, const void* W, const float* bias, void* out
     const long long wide_tiles = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
     if (N >= 256 && wide_tiles >= 96) return launch_wide<4>(X, W, bias, out, mode, M, N, K, ldo, rs, err, stream);
     return launch<128, 3>(X, W, bias, out, mode, M, N, K, ldo, rs, err, stream);
+}
+
+// The grouped product: the rows of X [M, K] are sorted by group and padded so that every tile of 128 rows belongs
+// to one group (tile_group [M / 128], negative for spare tiles); W [w_rows, w_cols] holds the groups' matrices one
+// below the other (b_row_step rows a group, b_k_step 0) or side by side along K (b_k_step columns a group, a
+// multiple of 8; b_row_step 0); N and K are ONE group's sizes.  Modes as mv_gemm_tc (no bias, no carried norm).
+// A tile's rows beyond its group's real rows hold whatever X holds there and give rows of ``out`` that nobody reads.
+MV_API int mv_gemm_tc_grouped(const void* X, const void* W, void* out, int mode, int M, int N, int K, int ldo,
+                              int w_rows, int w_cols, const int* tile_group, int b_row_step, int b_k_step, int* err,
+                              cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || M % BM || b_k_step % 8 || !tile_group || ((uintptr_t)X & 15) || ((uintptr_t)W & 15))
+        return (int)cudaErrorInvalidValue;
+    if (mode == 3 && (N % 32 || ldo % 2)) return (int)cudaErrorInvalidValue;
+    if (N <= 64)
+        return launch_grouped<64, 4>(X, W, out, mode, M, N, K, ldo, w_rows, w_cols, tile_group, b_row_step, b_k_step, err, stream);
+    return launch_grouped<128, 3>(X, W, out, mode, M, N, K, ldo, w_rows, w_cols, tile_group, b_row_step, b_k_step, err, stream);
 }

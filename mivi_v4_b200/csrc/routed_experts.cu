@@ -179,14 +179,20 @@ expert_rank_kernel(const int* __restrict__ pick, int total, int* __restrict__ ra
 template <typename T>
 __global__ void __launch_bounds__(128)
 expert_gather_kernel(const int* __restrict__ pick, const int* __restrict__ rank, const int* __restrict__ counts,
-                     const T* __restrict__ x, int top, int H, int* __restrict__ place, T* __restrict__ xs) {
+                     const int* __restrict__ offsets, const T* __restrict__ x, int top, int H, int* __restrict__ place,
+                     T* __restrict__ xs) {
     mv_pdl_begin();
     __shared__ float scratch[33];
     const int idx = blockIdx.x;
     const int e = pick[idx];
-    int before = 0;
-    for (int i = threadIdx.x; i < e; i += blockDim.x) before += counts[i];
-    const int p = (int)(mv_block_sum((float)before, scratch) + 0.5f) + rank[idx];       // exact: counts are far below 2^24
+    int p;
+    if (offsets) {
+        p = offsets[e] + rank[idx];                // where the expert's (padded) run of rows starts
+    } else {
+        int before = 0;
+        for (int i = threadIdx.x; i < e; i += blockDim.x) before += counts[i];
+        p = (int)(mv_block_sum((float)before, scratch) + 0.5f) + rank[idx];       // exact: counts are far below 2^24
+    }
     if (threadIdx.x == 0) place[idx] = p;
     const T* src = x + (size_t)(idx / top) * H;
     T* dst = xs + (size_t)p * H;
@@ -218,15 +224,57 @@ MV_API int mv_expert_rank(const int* pick, int total, int E, int* rank, int* cou
 }
 
 // x [N, H] in `dtype` -> xs [N * top, H] sorted by expert; place [N * top] says where each entry went
-MV_API int mv_expert_gather(const int* pick, const int* rank, const int* counts, const void* x, int dtype, int N, int top,
-                            int H, int* place, void* xs, cudaStream_t stream) {
+// offsets (or null): where every expert's run of rows starts (mv_expert_tiles), instead of the plain sums of counts
+MV_API int mv_expert_gather(const int* pick, const int* rank, const int* counts, const int* offsets, const void* x,
+                            int dtype, int N, int top, int H, int* place, void* xs, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (dtype == MV_DT_BF16)
-        mv_launch(expert_gather_kernel<__nv_bfloat16>, N * top, 128, 0, stream, pick, rank, counts, (const __nv_bfloat16*)x,
-                  top, H, place, (__nv_bfloat16*)xs);
+        mv_launch(expert_gather_kernel<__nv_bfloat16>, N * top, 128, 0, stream, pick, rank, counts, offsets,
+                  (const __nv_bfloat16*)x, top, H, place, (__nv_bfloat16*)xs);
     else
-        mv_launch(expert_gather_kernel<float>, N * top, 128, 0, stream, pick, rank, counts, (const float*)x, top, H, place,
-                  (float*)xs);
+        mv_launch(expert_gather_kernel<float>, N * top, 128, 0, stream, pick, rank, counts, offsets, (const float*)x, top, H,
+                  place, (float*)xs);
+    return mv_launch_status();
+}
+
+// Every expert's run of rows padded to whole tiles of `tile_rows`, so that a grouped product's tile never holds two
+// experts: offsets[e] = where expert e's run starts, tile_group[t] = the expert of tile t, -1 for the spare tiles
+// after the last run.  One block; the host needs to know nothing (n_tiles is an upper bound:
+// (entries + E * (tile_rows - 1)) / tile_rows).
+__global__ void __launch_bounds__(256)
+expert_tiles_kernel(const int* __restrict__ counts, int E, int tile_rows, int* __restrict__ offsets,
+                    int* __restrict__ tile_group, int n_tiles) {
+    mv_pdl_begin();
+    __shared__ int first_tile[RE_MAX_EXPERTS + 1];
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int e = 0; e < E; ++e) {
+            first_tile[e] = t;
+            offsets[e] = t * tile_rows;
+            t += (counts[e] + tile_rows - 1) / tile_rows;
+        }
+        first_tile[E] = t;
+    }
+    __syncthreads();
+    for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+        int g = -1;
+        if (t < first_tile[E]) {
+            int lo = 0, hi = E;                    // the last expert whose first tile is <= t and that has tiles
+            while (hi - lo > 1) {
+                const int mid = (lo + hi) >> 1;
+                if (first_tile[mid] <= t) lo = mid; else hi = mid;
+            }
+            g = lo;
+        }
+        tile_group[t] = g;
+    }
+}
+
+MV_API int mv_expert_tiles(const int* counts, int E, int tile_rows, int* offsets, int* tile_group, int n_tiles,
+                           cudaStream_t stream) {
+    if (E <= 0 || n_tiles <= 0) return 0;
+    if (E > RE_MAX_EXPERTS || tile_rows < 1) return (int)cudaErrorInvalidValue;
+    mv_launch(expert_tiles_kernel, 1, 256, 0, stream, counts, E, tile_rows, offsets, tile_group, n_tiles);
     return mv_launch_status();
 }
 

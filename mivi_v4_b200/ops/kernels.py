@@ -77,7 +77,8 @@ _SIGNATURES = {
         "mv_routed_glu": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
         "mv_scale_expert_columns": [_P, _I, _P, _I, _I, _I, _I, _P],
         "mv_expert_rank": [_P, _I, _I, _P, _P, _P],
-        "mv_expert_gather": [_P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+        "mv_expert_gather": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
+        "mv_expert_tiles": [_P, _I, _I, _P, _P, _I, _P],
         "mv_expert_combine": [_P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
         "mv_sample": [_P, _Q, _P, _I, _I, _F, _I, _F, _F, _F, _F, _F, _P, _P, _UQ, _P, _P, _P, _P, _P, _P, _P, _P],
     },
@@ -88,6 +89,7 @@ _SIGNATURES = {
         "mv_gemm_small_m_heads": [_P, _P, _P, _P, _F, _P, _I, _P, _P, _P, _I, _I, _P, _Q, _P, _I, _I, _I, _I,
                                   _P, _I, _I, _I, _F, _P, _Q, _P],
         "mv_gemm_tc": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P],
+        "mv_gemm_tc_grouped": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P, _I, _I, _P, _P],
         "mv_gemm_tc_pair": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _P],
         "mv_gemm_tc_swap": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _P, _P, _I, _P, _Q, _P, _P],
         "mv_gemm_tc_swap_shortconv": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _I, _I, _I, _F, _P, _Q,
@@ -718,32 +720,93 @@ def scale_expert_columns(h: torch.Tensor, dense: torch.Tensor, n_experts: int, f
     return h
 
 
+GROUPED_TILE_ROWS = 128
+
+
+def grouped_tiles(n_entries: int, n_experts: int) -> int:
+    """Tiles of ``GROUPED_TILE_ROWS`` rows that the sorted entries can need at most, every expert's run padded to
+    whole tiles."""
+    return (n_entries + n_experts * (GROUPED_TILE_ROWS - 1)) // GROUPED_TILE_ROWS + 1
+
+
 def expert_sort(pick: torch.Tensor, n_experts: int, x: torch.Tensor, rank: torch.Tensor, counts: torch.Tensor,
-                place: torch.Tensor, xs: torch.Tensor) -> None:
+                place: torch.Tensor, xs: torch.Tensor, offsets: Optional[torch.Tensor] = None,
+                tile_group: Optional[torch.Tensor] = None) -> None:
     """The (token, choice) entries of ``pick`` [N, top] sorted by expert (stable): ``counts`` [experts] entries an
-    expert, ``place`` [N * top] where each entry went, and the tokens' rows of ``x`` [N, H] copied to ``xs``
-    [N * top, H] in that order, so that an expert's rows lie together."""
+    expert, ``place`` [N * top] where each entry went, and the tokens' rows of ``x`` [N, H] copied to ``xs`` in that
+    order, so that an expert's rows lie together.  With ``offsets`` [experts] and ``tile_group`` [tiles] every
+    expert's run starts on a tile of ``GROUPED_TILE_ROWS`` rows (``xs`` then has tiles * that many rows, the rows
+    between runs are left as they are), ``offsets`` says where, and ``tile_group`` names each tile's expert (-1 for
+    the spare tiles at the end): what :func:`gemm_tc_grouped` takes."""
     N, top = pick.shape
     H = x.shape[1]
+    padded = offsets is not None
+    if padded != (tile_group is not None):
+        raise KernelError("expert_sort: offsets and tile_group come together")
+    rows = tile_group.numel() * GROUPED_TILE_ROWS if padded else N * top
+    if padded and tile_group.numel() < grouped_tiles(N * top, n_experts):
+        raise KernelError(f"expert_sort: {tile_group.numel()} tiles for {N * top} entries of {n_experts} experts")
     _check(_fn("core", "mv_expert_rank")(
         _need(pick, "picks", torch.int32), N * top, int(n_experts), _need(rank, "ranks", torch.int32, (N * top,)),
         _need(counts, "counts", torch.int32, (n_experts,)), _stream()), "mv_expert_rank")
+    if padded:
+        _check(_fn("core", "mv_expert_tiles")(
+            counts.data_ptr(), int(n_experts), GROUPED_TILE_ROWS, _need(offsets, "offsets", torch.int32, (n_experts,)),
+            _need(tile_group, "tile groups", torch.int32), tile_group.numel(), _stream()), "mv_expert_tiles")
     _check(_fn("core", "mv_expert_gather")(
-        pick.data_ptr(), rank.data_ptr(), counts.data_ptr(), _need(x, "expert_sort rows", None, (N, H)), _dt(x), N, top, H,
-        _need(place, "places", torch.int32, (N * top,)), _need(xs, "sorted rows", x.dtype, (N * top, H)), _stream()),
+        pick.data_ptr(), rank.data_ptr(), counts.data_ptr(), offsets.data_ptr() if padded else None,
+        _need(x, "expert_sort rows", None, (N, H)), _dt(x), N, top, H,
+        _need(place, "places", torch.int32, (N * top,)), _need(xs, "sorted rows", x.dtype, (rows, H)), _stream()),
         "mv_expert_gather")
     account(N * (1 + top) * H * x.element_size())
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, tile_group: torch.Tensor, n: int, k: int, *,
+                    row_step: int = 0, k_step: int = 0, swiglu: bool = False, active_rows: Optional[int] = None) -> torch.Tensor:
+    """One product for many groups, on the tcgen05 tensor cores (bfloat16): the rows of ``x`` [tiles * 128, k] are
+    sorted by group with every group's run padded to whole tiles (:func:`expert_sort`), ``tile_group`` names each
+    tile's group (negative: nothing to do), and ``w`` holds the groups' [n, k] matrices one below the other
+    (``row_step`` rows a group) or side by side along its columns (``k_step`` columns a group).  ``out``
+    [tiles * 128, n] float32 or bfloat16, or with ``swiglu`` bfloat16 [tiles * 128, n / 2] from rows of ``w`` that
+    alternate in groups of 16 gate and 16 up rows.  ``active_rows``: rows that belong to a group, for the profile's
+    accounts."""
+    M = x.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        raise KernelError(f"gemm_tc_grouped: operands must be bfloat16, got {x.dtype} and {w.dtype}")
+    if M != tile_group.numel() * GROUPED_TILE_ROWS or x.shape[1] != k:
+        raise KernelError(f"gemm_tc_grouped: x is {tuple(x.shape)} for {tile_group.numel()} tiles and k = {k}")
+    if k % 8 or k_step % 8 or (row_step and k_step):
+        raise KernelError(f"gemm_tc_grouped: k {k} and k_step {k_step} must be multiples of 8; one of row_step and k_step")
+    if swiglu:
+        if n % 32:
+            raise KernelError(f"gemm_tc_grouped: the SwiGLU epilogue needs rows in groups of 32, got {n}")
+        mode, ldo = 3, n // 2
+        _need(out, "gemm out", torch.bfloat16, (M, n // 2))
+    else:
+        mode, ldo = (0 if out.dtype == torch.float32 else 1), n
+        _need(out, "gemm out", None, (M, n))
+        _dt(out)
+    _check(_fn("bf16", "mv_gemm_tc_grouped")(
+        _need(x, "gemm x"), _need(w, "gemm w"), out.data_ptr(), mode, M, int(n), int(k), ldo, w.shape[0], w.shape[1],
+        _need(tile_group, "tile groups", torch.int32), int(row_step), int(k_step), _error_flag(x.device).data_ptr(),
+        _stream()), "mv_gemm_tc_grouped")
+    rows = M if active_rows is None else active_rows
+    account(rows * (k * 2 + ldo * out.element_size()) + _nbytes(w), 2 * rows * n * k)
+    return out
 
 
 def expert_combine(ys: torch.Tensor, place: torch.Tensor, pick_w: torch.Tensor, shared: Optional[torch.Tensor],
                    gate: Optional[torch.Tensor], out: torch.Tensor, accumulate: bool) -> torch.Tensor:
     """out[n] (+)= sum_k pick_w[n, k] * ys[place[n * top + k]] (+ gate[n] * shared[n]), float32: the chosen experts'
-    results gathered back in the order of the choices.  ``gate`` [N, 1] may be a column of a wider matrix."""
+    results gathered back in the order of the choices.  ``gate`` [N, 1] may be a column of a wider matrix.  ``ys``
+    has at least N * top rows (more where the experts' runs are padded)."""
     N, H = out.shape
     top = pick_w.shape[1]
+    if ys.shape[0] < N * top:
+        raise KernelError(f"expert_combine: {ys.shape[0]} result rows for {N * top} entries")
     gp, ldg = _cols(gate, "shared gate", N, 1) if gate is not None else (None, 0)
     _check(_fn("core", "mv_expert_combine")(
-        _need(ys, "expert results", torch.float32, (N * top, H)), _need(place, "places", torch.int32, (N * top,)),
+        _need(ys, "expert results", torch.float32, (None, H)), _need(place, "places", torch.int32, (N * top,)),
         _need(pick_w, "pick weights", torch.float32, (N, top)), _need(shared, "shared result", torch.float32, (N, H), True),
         gp, ldg, _need(out, "combine out", torch.float32), N, top, H, int(bool(accumulate)), _stream()), "mv_expert_combine")
     account(N * H * 4 * (top + 2 + (1 if shared is not None else 0)))

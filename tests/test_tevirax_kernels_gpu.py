@@ -475,3 +475,48 @@ def test_one_token_a_sequence_convolution_and_step_size_in_one_kernel(taps):
     if taps > 1:
         assert state[1].abs().max() == 0
         close(state[0], u[1, T - (taps - 1):, 2:2 + C], 1e-6, "kept inputs")
+
+
+@pytest.mark.parametrize("E,top,ff,H,N", [(4, 2, 32, 64, 300), (16, 4, 64, 128, 700), (6, 1, 16, 40, 130), (3, 2, 48, 72, 5)])
+def test_grouped_products_over_rows_sorted_by_expert(E, top, ff, H, N):
+    """Every expert's run of rows starts on a tile; one product takes each tile's rows through ITS expert's gate and
+    up rows (with the activation), one through its down columns; experts that nobody chose, and runs of one row."""
+    k = K()
+    g = torch.Generator().manual_seed(E * 10 + top)
+    x = torch.randn(N, H, generator=g).bfloat16()
+    choice = torch.stack([torch.randperm(E - 1, generator=g)[:top] for _ in range(N)]).int()     # the last expert: never
+    if N > 100:
+        choice[7, 0] = E - 1                                                                      # but once
+        choice[7, 1:] = torch.arange(top - 1)
+    w_gate, w_up = (torch.randn(E, ff, H, generator=g) / H ** 0.5).bfloat16(), (torch.randn(E, ff, H, generator=g) / H ** 0.5).bfloat16()
+    w_down = (torch.randn(E, H, ff, generator=g) / ff ** 0.5).bfloat16()
+    w_gu = torch.stack([w_gate.view(E, ff // 16, 16, H), w_up.view(E, ff // 16, 16, H)], dim=2).reshape(E * 2 * ff, H).contiguous()
+    w_dn = torch.cat(list(w_down), dim=1).contiguous()                                            # [H, E * ff]
+    tiles = k.grouped_tiles(N * top, E)
+    rows = tiles * k.GROUPED_TILE_ROWS
+    pick = choice.to(DEV)
+    rank, place = (torch.empty(N * top, dtype=torch.int32, device=DEV) for _ in range(2))
+    counts, offsets = (torch.empty(E, dtype=torch.int32, device=DEV) for _ in range(2))
+    tile_group = torch.empty(tiles, dtype=torch.int32, device=DEV)
+    xs = torch.full((rows, H), float("nan"), dtype=torch.bfloat16, device=DEV)                   # the padding stays as it is
+    k.expert_sort(pick, E, x.to(DEV), rank, counts, place, xs, offsets, tile_group)
+    cnt = torch.bincount(choice.flatten().long(), minlength=E)
+    assert counts.cpu().tolist() == cnt.tolist()
+    tiles_of = (cnt + 127) // 128
+    want_off = torch.cat([torch.zeros(1, dtype=torch.long), tiles_of.cumsum(0)[:-1]]) * 128
+    assert offsets.cpu().tolist() == want_off.tolist()
+    want_groups = sum(([e] * int(t) for e, t in enumerate(tiles_of)), [])
+    assert tile_group.cpu().tolist() == want_groups + [-1] * (tiles - len(want_groups))
+    pl = place.cpu().long()
+    assert torch.equal(xs.cpu()[pl].float(), x[torch.arange(N * top) // top].float())
+    hs = torch.full((rows, ff), float("nan"), dtype=torch.bfloat16, device=DEV)
+    k.gemm_tc_grouped(xs, w_gu.to(DEV), hs, tile_group, 2 * ff, H, row_step=2 * ff, swiglu=True)
+    ys = torch.full((rows, H), float("nan"), device=DEV)
+    k.gemm_tc_grouped(hs, w_dn.to(DEV), ys, tile_group, H, ff, k_step=ff)
+    e_of = choice.flatten().long()
+    xe = x[torch.arange(N * top) // top].double()
+    gate = torch.einsum("nh,nfh->nf", xe, w_gate.double()[e_of])
+    up = torch.einsum("nh,nfh->nf", xe, w_up.double()[e_of])
+    hid = (P.silu(gate) * up).bfloat16().double()
+    close(hs.cpu()[pl], hid, 1e-2, "gated activations")
+    close(ys.cpu()[pl], torch.einsum("nf,nhf->nh", hid, w_down.double()[e_of]), 1e-2, "down")
