@@ -32,6 +32,34 @@ causal_conv_silu_kernel(const float* __restrict__ u, int ld, const float* __rest
     out[idx] = acc / (1.0f + expf(-acc));
 }
 
+// The same with four consecutive channels a thread (16-byte loads): C, ld and the pointers allow it.
+__global__ void __launch_bounds__(256)
+causal_conv_silu_vec_kernel(const float* __restrict__ u, int ld, const float* __restrict__ taps,
+                            const float* __restrict__ bias, const float* __restrict__ state,
+                            const int* __restrict__ seq_of, const int* __restrict__ cu, const int* __restrict__ slots,
+                            float* __restrict__ out, long long total4, int C, int K) {
+    mv_pdl_begin();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total4) return;
+    const int C4 = C >> 2;
+    const int n = (int)(idx / C4), c = (int)(idx - (long long)n * C4) << 2;
+    const int b = seq_of[n];
+    const int li = n - cu[b];
+    const float* st = state + (size_t)mv_read_slot(slots[b]) * (K - 1) * C;
+    float4 acc = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* tp = taps + (size_t)c * K;                  // the four channels' taps: 4 K consecutive values
+    for (int j = 0; j < K; ++j) {
+        const int back = K - 1 - j;
+        const float4 x = li >= back ? *reinterpret_cast<const float4*>(u + (size_t)(n - back) * ld + c)
+                                    : *reinterpret_cast<const float4*>(st + (size_t)(li + j) * C + c);
+        acc.x = fmaf(tp[j], x.x, acc.x); acc.y = fmaf(tp[K + j], x.y, acc.y);
+        acc.z = fmaf(tp[2 * K + j], x.z, acc.z); acc.w = fmaf(tp[3 * K + j], x.w, acc.w);
+    }
+    acc.x = acc.x / (1.0f + expf(-acc.x)); acc.y = acc.y / (1.0f + expf(-acc.y));
+    acc.z = acc.z / (1.0f + expf(-acc.z)); acc.w = acc.w / (1.0f + expf(-acc.w));
+    *reinterpret_cast<float4*>(out + (size_t)n * C + c) = acc;
+}
+
 // After the step the kept inputs are the last taps - 1 of (kept inputs, the step's inputs).  One thread a
 // (sequence, channel) reads all it needs before it writes.
 __global__ void __launch_bounds__(256)
@@ -124,8 +152,14 @@ MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const 
     if (N <= 0 || n_seqs <= 0) return 0;
     if (K < 1 || K > SP_MAX_TAPS || C < 1) return (int)cudaErrorInvalidValue;
     const long long total = (long long)N * C;
-    mv_launch(causal_conv_silu_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, u, ld, taps, bias,
-              (const float*)state, seq_of, cu, slots, out, total, C, K);
+    const bool wide = C % 4 == 0 && ld % 4 == 0 && N >= 64 &&
+                      (((uintptr_t)u | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out) & 15) == 0;
+    if (wide)
+        mv_launch(causal_conv_silu_vec_kernel, (unsigned)((total / 4 + 255) / 256), 256, 0, stream, u, ld, taps, bias,
+                  (const float*)state, seq_of, cu, slots, out, total / 4, C, K);
+    else
+        mv_launch(causal_conv_silu_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, u, ld, taps, bias,
+                  (const float*)state, seq_of, cu, slots, out, total, C, K);
     if (K > 1)
         mv_launch(causal_conv_state_kernel, dim3((C + 255) / 256, n_seqs), 256, 0, stream, u, ld, state, cu, slots, C, K);
     return mv_launch_status();

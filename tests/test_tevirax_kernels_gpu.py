@@ -520,3 +520,34 @@ def test_grouped_products_over_rows_sorted_by_expert(E, top, ff, H, N):
     hid = (P.silu(gate) * up).bfloat16().double()
     close(hs.cpu()[pl], hid, 1e-2, "gated activations")
     close(ys.cpu()[pl], torch.einsum("nf,nhf->nh", hid, w_down.double()[e_of]), 1e-2, "down")
+
+
+@pytest.mark.parametrize("taps", [1, 3, 4])
+def test_causal_convolution_of_long_steps_four_channels_a_thread(taps):
+    k = K()
+    C = 40
+    g = torch.Generator().manual_seed(taps + 70)
+    lens = [130, 1, 67]
+    us = [torch.randn(n, 4 + C, generator=g, dtype=F64) for n in lens]
+    w, bias = torch.randn(C, taps, generator=g, dtype=F64), torch.randn(C, generator=g, dtype=F64)
+    want = torch.cat([P.silu(P.causal_taps(u[:, 4:], w, bias)) for u in us])
+    for cuts in ([1.0], [0.5, 0.5]):                      # whole, and each sequence in two steps of about half
+        state = torch.zeros(3, max(taps - 1, 0), C, device=DEV)
+        done = [0] * len(lens)
+        outs = [[] for _ in lens]
+        for frac in cuts:
+            part = [(d, n if frac == 1.0 or d else max(1, n // 2)) for d, n in zip(done, lens)]
+            part = [(d, (n - d) if d else m) for (d, m), n in zip(part, lens)]
+            rows = torch.cat([u[d:d + m] for u, (d, m) in zip(us, part)])
+            cu, seq_of = [0], []
+            for i, (_, m) in enumerate(part):
+                cu.append(cu[-1] + m)
+                seq_of += [i] * m
+            out = torch.full((rows.shape[0], C), float("nan"), device=DEV)
+            k.causal_conv_silu(dev(rows)[:, 4:], dev(w), dev(bias), state, i32(seq_of), i32(cu), i32([2, 0, 1]), out, len(lens))
+            for i, (d, m) in enumerate(part):
+                outs[i].append(out[cu[i]:cu[i + 1]])
+                done[i] = d + m
+            if all(d == n for d, n in zip(done, lens)):
+                break
+        close(torch.cat([torch.cat(o) for o in outs]), want, 1e-5, f"taps {taps} cuts {cuts}")
