@@ -48,12 +48,28 @@ causal_conv_silu_vec_kernel(const float* __restrict__ u, int ld, const float* __
     const float* st = state + (size_t)mv_read_slot(slots[b]) * (K - 1) * C;
     float4 acc = bias ? *reinterpret_cast<const float4*>(bias + c) : make_float4(0.f, 0.f, 0.f, 0.f);
     const float* tp = taps + (size_t)c * K;                  // the four channels' taps: 4 K consecutive values
-    for (int j = 0; j < K; ++j) {
-        const int back = K - 1 - j;
-        const float4 x = li >= back ? *reinterpret_cast<const float4*>(u + (size_t)(n - back) * ld + c)
-                                    : *reinterpret_cast<const float4*>(st + (size_t)(li + j) * C + c);
-        acc.x = fmaf(tp[j], x.x, acc.x); acc.y = fmaf(tp[K + j], x.y, acc.y);
-        acc.z = fmaf(tp[2 * K + j], x.z, acc.z); acc.w = fmaf(tp[3 * K + j], x.w, acc.w);
+    if (K == 4) {
+        // four taps a channel: a channel's taps are one 16-byte load
+        const float4 t0 = *reinterpret_cast<const float4*>(tp), t1 = *reinterpret_cast<const float4*>(tp + 4);
+        const float4 t2 = *reinterpret_cast<const float4*>(tp + 8), t3 = *reinterpret_cast<const float4*>(tp + 12);
+        const float w0[4] = {t0.x, t0.y, t0.z, t0.w}, w1[4] = {t1.x, t1.y, t1.z, t1.w};
+        const float w2[4] = {t2.x, t2.y, t2.z, t2.w}, w3[4] = {t3.x, t3.y, t3.z, t3.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int back = 3 - j;
+            const float4 x = li >= back ? *reinterpret_cast<const float4*>(u + (size_t)(n - back) * ld + c)
+                                        : *reinterpret_cast<const float4*>(st + (size_t)(li + j) * C + c);
+            acc.x = fmaf(w0[j], x.x, acc.x); acc.y = fmaf(w1[j], x.y, acc.y);
+            acc.z = fmaf(w2[j], x.z, acc.z); acc.w = fmaf(w3[j], x.w, acc.w);
+        }
+    } else {
+        for (int j = 0; j < K; ++j) {
+            const int back = K - 1 - j;
+            const float4 x = li >= back ? *reinterpret_cast<const float4*>(u + (size_t)(n - back) * ld + c)
+                                        : *reinterpret_cast<const float4*>(st + (size_t)(li + j) * C + c);
+            acc.x = fmaf(tp[j], x.x, acc.x); acc.y = fmaf(tp[K + j], x.y, acc.y);
+            acc.z = fmaf(tp[2 * K + j], x.z, acc.z); acc.w = fmaf(tp[3 * K + j], x.w, acc.w);
+        }
     }
     acc.x = acc.x / (1.0f + expf(-acc.x)); acc.y = acc.y / (1.0f + expf(-acc.y));
     acc.z = acc.z / (1.0f + expf(-acc.z)); acc.w = acc.w / (1.0f + expf(-acc.w));
@@ -153,7 +169,7 @@ MV_API int mv_causal_conv_silu(const float* u, int ld, const float* taps, const 
     if (K < 1 || K > SP_MAX_TAPS || C < 1) return (int)cudaErrorInvalidValue;
     const long long total = (long long)N * C;
     const bool wide = C % 4 == 0 && ld % 4 == 0 && N >= 64 &&
-                      (((uintptr_t)u | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out) & 15) == 0;
+                      (((uintptr_t)u | (uintptr_t)bias | (uintptr_t)state | (uintptr_t)out | (uintptr_t)taps) & 15) == 0;
     if (wide)
         mv_launch(causal_conv_silu_vec_kernel, (unsigned)((total / 4 + 255) / 256), 256, 0, stream, u, ld, taps, bias,
                   (const float*)state, seq_of, cu, slots, out, total / 4, C, K);
