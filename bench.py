@@ -218,13 +218,13 @@ def tevirax_config(width, layers, heads, kv_heads, ff, vocab):
     2 of 4 groups, and a shared one)."""
     mamba = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}
     par = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
-                    "rot": {"dims": 32, "base": 500000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}},
+                    "rot": {"dims": 32, "base": 1000000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}},
            "right": {"heads": max(1, width // 256), "dim": 128, "vdim": 256, "gate_cap": 15.0},
            "left_scale": 1.0, "right_scale": 1.0}
     moe = {"kind": "moe", "expert": {"ff": ff // 8}, "shared": {"ff": ff // 8},
            "router": {"experts": 16, "top": 4, "groups": {"count": 4, "keep": 2}}}
     return {"architecture": "Tevirax", "vocab": vocab, "width": width, "max_positions": 4096, "norm": {"eps": 1e-6},
-            "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 30.0,
+            "embedding": {"scale": float(width) ** 0.5}, "logit_softcap": 50.0,
             "layers": [{"type": "parallel" if i % 3 == 2 else "mamba2", "mixer": par if i % 3 == 2 else mamba,
                         "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe} for i in range(layers)]}
 

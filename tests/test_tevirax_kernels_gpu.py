@@ -195,7 +195,7 @@ def test_step_size():
 
 
 # ------------------------------------------------------------------------------------------ experts
-@pytest.mark.parametrize("E,count,keep,top,shared", [(16, 2, 1, 4, True), (12, 3, 2, 3, True), (5, 1, 1, 1, False),
+@pytest.mark.parametrize("E,count,keep,top,shared", [(16, 4, 1, 3, True), (12, 3, 2, 3, True), (5, 1, 1, 1, False),
                                                       (8, 4, 1, 2, False), (64, 8, 3, 6, True), (6, 6, 2, 2, False)])
 def test_router_and_routed_activation(E, count, keep, top, shared):
     k = K()

@@ -78,7 +78,7 @@ TEV_B = {"architecture": "Tevirax", "vocab": 131, "width": 48, "max_positions": 
 TEV_C = {"architecture": "Tevirax", "vocab": 200, "width": 128, "max_positions": 600, "norm": {"eps": 1e-6},
          "embedding": {"scale": 11.0}, "logit_softcap": 50.0,
          "layers": [_mamba(2, 40, 72, 1, 3, 2, _moe(8, 32, 2, 4, 1, 48)),
-                    _par(_left(4, 1, 32, 64, 64, _yarn(16, 500.0, 2.0, 128, 8.0, 2.0), 0.17), _right(1, 136, 17, 12.0), 0.8, 1.1,
+                    _par(_left(4, 1, 32, 64, 64, _yarn(16, 500.0, 2.0, 128, 8.0, 2.0), 0.17), _right(1, 136, 17, 9.0), 0.6, 1.4,
                          _moe(6, 16, 4, 2, 2, 8)),
                     _mamba(1, 24, 136, 1, 4, 1, None),
                     _par(_left(2, 1, 64, 32, 150, _yarn(64, 50000.0, 8.0, 256), 0.125), _right(2, 72, 40, 30.0), 1.2, 0.9,
